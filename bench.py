@@ -1,0 +1,275 @@
+#!/usr/bin/env python
+"""Benchmark of the MXFP4 hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload gemm|quantize] [--impl ours|reference]
+
+One JSON line on stdout (rank 0).  Workloads:
+
+  gemm      one step = quant_matmul of bf16 activations [8192, 4096] with an MXFP4 weight [11008, 4096]
+            (Llama-2-7B gate/up projection shape of the GEMM sweep); metric = TFLOP/s per GPU counted as
+            2*M*N*K.  This is the default.
+  quantize  one step = MXFP4Quantizer.quantize of the 7 weight matrices of one Llama-2-7B decoder layer
+            (4 x 4096x4096, 2 x 11008x4096, 1 x 4096x11008; 405 MB of bf16, larger than L2);
+            metric = GB/s of algorithmic traffic (2.53125 bytes per element).
+
+Multi-GPU: every rank runs the same per-GPU workload on its own data (weak scaling, no data-path
+collective: quantisation blocks and GEMM tiles are independent); `value` is the sum over ranks of
+work divided by the slowest rank's device time.
+
+`--impl reference` times the CPU oracle port of the reference's own path (dequantise-then-matmul,
+resp. the PyTorch quantiser restated in C) on this box's host cores.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+sys.path.insert(0, os.path.join(ROOT, "moizmxfp4-public_b200"))
+
+import torch  # noqa: E402
+
+QUANT_BYTES_PER_ELEM = 2.0 + 0.5 + 1.0 / 32.0
+LAYER_SHAPES = [(4096, 4096)] * 4 + [(11008, 4096)] * 2 + [(4096, 11008)]
+GEMM_M, GEMM_N, GEMM_K = 8192, 11008, 4096
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        with open(p) as f:
+            d = json.load(f)
+        return dict(hbm_gbs=d["hbm_gbs"], bf16_tflops=d["bf16_tflops"], source="measured")
+    return dict(hbm_gbs=6650.0, bf16_tflops=1590.0, source="fallback")
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons of one GPU with nvidia-smi while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.samples, self.stop = index, [], threading.Event()
+        self.thread = threading.Thread(target=self.run, daemon=True)
+
+    def run(self):
+        while not self.stop.is_set():
+            try:
+                out = subprocess.run(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-i", str(self.index)],
+                                     capture_output=True, text=True, timeout=5).stdout.strip()
+                if out:
+                    self.samples.append([c.strip() for c in out.split(",")])
+            except Exception:
+                pass
+            self.stop.wait(0.1)
+
+    def __enter__(self):
+        self.thread.start()
+        return self
+
+    def __exit__(self, *a):
+        self.stop.set()
+        self.thread.join(timeout=6)
+
+    def summary(self):
+        mhz = sorted(int(s[0]) for s in self.samples if s[0].isdigit())
+        reasons = set()
+        for s in self.samples:
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), s[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        mx = [int(s[1]) for s in self.samples if s[1].isdigit()]
+        return {"sm_mhz": mhz[len(mhz) // 2] if mhz else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(self.samples)}
+
+
+def weight(N, K, seed, outliers=False):
+    g = torch.Generator().manual_seed(seed)
+    w = torch.randn(N, K, generator=g) * 0.02
+    if outliers:
+        idx = torch.randperm(N * K, generator=g)[: int(0.001 * N * K)]
+        w.view(-1)[idx] *= 50
+    return w.to(torch.bfloat16)
+
+
+def dist_setup(n_gpus):
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world > 1:
+        import torch.distributed as dist
+        torch.cuda.set_device(local)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    return rank, world, local
+
+
+def max_over_ranks(ms, world, device):
+    if world == 1:
+        return ms
+    import torch.distributed as dist
+    t = torch.tensor([ms], dtype=torch.float64, device=device)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def barrier(world):
+    if world > 1:
+        import torch.distributed as dist
+        dist.barrier()
+    torch.cuda.synchronize()
+
+
+# ------------------------------------------------------------------------------------------------
+# quantize workload
+# ------------------------------------------------------------------------------------------------
+def run_quantize(args, rank, world, local):
+    from mxfp4.quantizer import MXFP4Quantizer
+    from mxfp4 import _capi
+    dev = torch.device("cuda", local)
+    q = MXFP4Quantizer(32, "e8m0")
+    host = [weight(n, k, 100 * rank + i).pin_memory() for i, (n, k) in enumerate(LAYER_SHAPES)]
+    devw = [h.to(dev) for h in host]
+    elems = sum(n * k for n, k in LAYER_SHAPES)
+    launches = 0
+
+    def step():
+        out = [q.quantize(w) for w in devw]
+        return out
+
+    for _ in range(args.warmup):
+        step()
+    barrier(world)
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+    with ClockSampler(local) as cs:
+        ev[0].record()
+        for _ in range(args.steps):
+            step()
+            launches += len(devw)
+        ev[1].record()
+        torch.cuda.synchronize()
+        ms = ev[0].elapsed_time(ev[1])
+        if ms < 300:   # keep the GPU busy long enough for a few clock samples
+            t_end = time.time() + 0.5
+            while time.time() < t_end:
+                step()
+            torch.cuda.synchronize()
+    ms = max_over_ranks(ms, world, dev)
+    barrier(world)
+    ms_per_step = ms / args.steps
+    value = world * elems * QUANT_BYTES_PER_ELEM / (ms_per_step * 1e-3) / 1e9
+
+    # per-launch time of the dominant kernel (the largest matrix), events on the launching stream
+    big = devw[4]
+    reps = 20
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    others = [devw[5], devw[6], devw[0], devw[1]]
+    torch.cuda.synchronize()
+    tot = 0.0
+    for i in range(reps):
+        q.quantize(others[i % 4])                # evicts `big` from L2 between timed launches (4 x >= 33 MB)
+        q.quantize(others[(i + 1) % 4])
+        e0.record()
+        q.quantize(big)
+        e1.record()
+        torch.cuda.synchronize()
+        tot += e0.elapsed_time(e1)
+    k_ms = tot / reps
+    k_bytes = big.numel() * QUANT_BYTES_PER_ELEM
+    pk = peaks()
+    roof = {"bound": "hbm", "kernel": "quantize_bf16_b32_kernel [11008x4096]", "achieved": k_bytes / (k_ms * 1e-3) / 1e9,
+            "peak": pk["hbm_gbs"], "unit": "GB/s", "peak_source": pk["source"], "traffic": None}
+    roof["frac"] = roof["achieved"] / roof["peak"]
+
+    # end to end through the public API with host buffers
+    e2e_ms = None
+    outs_host = [(torch.empty(n, k // 2, dtype=torch.uint8).pin_memory(), torch.empty(n, k // 32, dtype=torch.uint8).pin_memory())
+                 for n, k in LAYER_SHAPES]
+    stage = [torch.empty_like(w) for w in devw]
+
+    def e2e_step():
+        for h, d, (hp, hs) in zip(host, stage, outs_host):
+            d.copy_(h, non_blocking=True)
+            p, s = q.quantize(d)
+            hp.copy_(p, non_blocking=True)
+            hs.copy_(s, non_blocking=True)
+    for _ in range(2):
+        e2e_step()
+    barrier(world)
+    e0.record()
+    for _ in range(args.steps):
+        e2e_step()
+    e1.record()
+    torch.cuda.synchronize()
+    e2e_ms = max_over_ranks(e0.elapsed_time(e1), world, dev) / args.steps
+    barrier(world)
+    h2d = elems * 2
+    d2h = elems // 2 + elems // 32
+    res = {"metric": "mxfp4_quantize_hbm_gbs", "value": value, "unit": "GB/s", "ms_per_step": ms_per_step,
+           "config": {"workload": "quantize: one Llama-2-7B decoder layer (4x4096x4096, 2x11008x4096, 1x4096x11008 bf16), block 32, e8m0",
+                      "elements_per_step": elems, "l2": "inputs (405 MB per step) larger than L2"},
+           "dtype": "bf16->fp4(e2m1-like codes)+e8m0", "roofline": roof, "gpu_launches": launches,
+           "e2e": {"value": world * elems * QUANT_BYTES_PER_ELEM / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s",
+                   "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+           "clocks": cs.summary()}
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        res["cpu_baseline"] = cpu_quantize_baseline()
+    return res
+
+
+def cpu_quantize_baseline(budget_s=12.0):
+    from oracle import oracle
+    w = weight(4096, 4096, 0, True)
+    oracle.quantize(w[:64])
+    n, t0 = 0, time.time()
+    while True:
+        oracle.quantize(w)
+        n += 1
+        if time.time() - t0 > budget_s or n >= 20:
+            break
+    dt = (time.time() - t0) / n
+    return {"value": w.numel() * QUANT_BYTES_PER_ELEM / dt / 1e9, "unit": "GB/s", "cores": oracle.num_threads(), "kind": "port",
+            "sample": f"{n} x quantize of one 4096x4096 bf16 matrix (C restatement of the reference quantiser, OpenMP)"}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--workload", default=os.environ.get("MXFP4_BENCH_WORKLOAD", "quantize"), choices=["quantize", "gemm"])
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+
+    if args.impl == "reference":
+        rank = int(os.environ.get("RANK", "0"))
+        if rank != 0:
+            return
+        base = cpu_quantize_baseline(budget_s=max(5.0, 2.0 * args.steps))
+        out = {"impl": "reference", "metric": "mxfp4_quantize_hbm_gbs", "value": base["value"], "unit": "GB/s", "n_gpus": args.gpus,
+               "steps": args.steps, "warmup": args.warmup, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+               "dtype": "f32 arithmetic on bf16 input", "data": "synthetic", "config": {"workload": "quantize (bounded sample: one 4096x4096 matrix per step)"},
+               "cpu_baseline": base, "e2e": {"value": base["value"], "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+        print(json.dumps(out))
+        return
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (the product has no CPU path); use --impl reference for the CPU baseline")
+    rank, world, local = dist_setup(args.gpus)
+    res = run_quantize(args, rank, world, local)
+    res.update({"n_gpus": world, "steps": args.steps, "warmup": args.warmup, "higher_is_better": True, "scaling": "weak",
+                "vs_baseline": None, "data": "synthetic"})
+    if rank == 0:
+        print(json.dumps(res))
+    if world > 1:
+        import torch.distributed as dist
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

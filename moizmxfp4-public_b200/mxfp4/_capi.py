@@ -1,0 +1,145 @@
+"""ctypes binding of libmxfp4_b200.so -- the only compute backend of this package.
+
+There is no CPU implementation and no alternative GPU path: if the shared library is missing or a
+tensor is not on a CUDA device, the call raises.  Build the library with
+``python moizmxfp4-public_b200/build.py``.
+"""
+import ctypes
+import os
+
+import torch
+
+_LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "_lib", "libmxfp4_b200.so")
+_lib = None
+
+DT = {torch.bfloat16: 0, torch.float16: 1, torch.float32: 2}
+SF = {"e8m0": 0, "bf16": 1}
+GEMM_EXACT, GEMM_FAST = 0, 1
+
+
+class MXFP4BackendError(RuntimeError):
+    """A C-ABI call returned a non-zero status."""
+
+
+def lib_path() -> str:
+    return _LIB_PATH
+
+
+def load():
+    """Load the shared library once; raise loudly if it has not been built."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(_LIB_PATH):
+        raise RuntimeError(
+            f"mxfp4: CUDA backend library not found at {_LIB_PATH}. Build it with "
+            "`python moizmxfp4-public_b200/build.py` (needs nvcc). This package has no CPU or Triton fallback.")
+    L = ctypes.CDLL(_LIB_PATH)
+    i64, vp, ci = ctypes.c_int64, ctypes.c_void_p, ctypes.c_int
+    L.mxfp4_version.restype = ci
+    L.mxfp4_last_error.argtypes = [ctypes.c_char_p, ctypes.c_size_t]
+    L.mxfp4_last_error.restype = None
+    L.mxfp4_device_info.argtypes = [ctypes.POINTER(ci)] * 3
+    L.mxfp4_quantize.argtypes = [vp, ci, i64, i64, i64, ci, ci, vp, vp, vp]
+    L.mxfp4_dequantize.argtypes = [vp, vp, ci, i64, i64, ci, vp, ci, vp]
+    for name in ("mxfp4_device_info", "mxfp4_quantize", "mxfp4_dequantize"):
+        getattr(L, name).restype = ci
+    if hasattr(L, "mxfp4_gemm"):
+        L.mxfp4_act_quantize.argtypes = [vp, i64, i64, i64, vp, vp, vp]
+        L.mxfp4_act_quantize.restype = ci
+        L.mxfp4_prepare_weight_scales.argtypes = [vp, i64, i64, vp, vp]
+        L.mxfp4_prepare_weight_scales.restype = ci
+        L.mxfp4_prepared_scales_bytes.argtypes = [i64, i64]
+        L.mxfp4_prepared_scales_bytes.restype = i64
+        L.mxfp4_gemm_workspace_bytes.argtypes = [i64, i64, i64, ci]
+        L.mxfp4_gemm_workspace_bytes.restype = i64
+        L.mxfp4_gemm.argtypes = [vp, i64, vp, vp, vp, vp, i64, i64, i64, i64, ci, vp, i64, vp, vp]
+        L.mxfp4_gemm.restype = ci
+    _lib = L
+    return L
+
+
+def last_error() -> str:
+    buf = ctypes.create_string_buffer(512)
+    load().mxfp4_last_error(buf, 512)
+    return buf.value.decode("utf-8", "replace")
+
+
+def check(rc: int, what: str):
+    if rc != 0:
+        raise MXFP4BackendError(f"{what} failed (status {rc}): {last_error()}")
+
+
+def require_cuda(t: torch.Tensor, what: str):
+    if not t.is_cuda:
+        raise RuntimeError(f"mxfp4: {what} needs a CUDA tensor (got device '{t.device}'); "
+                           "the sm_100a backend is the only backend and there is no CPU fallback")
+
+
+def stream_ptr(device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def device_info():
+    maj, mnr, sms = ctypes.c_int(), ctypes.c_int(), ctypes.c_int()
+    check(load().mxfp4_device_info(ctypes.byref(maj), ctypes.byref(mnr), ctypes.byref(sms)), "mxfp4_device_info")
+    return maj.value, mnr.value, sms.value
+
+
+# ---------------------------------------------------------------------------------------------
+# Tensor-level wrappers.  Each one validates on the host, allocates outputs with torch, and
+# enqueues on torch's current stream of the tensor's device.
+# ---------------------------------------------------------------------------------------------
+def quantize(x: torch.Tensor, block_size: int, scale_format: str):
+    require_cuda(x, "MXFP4Quantizer.quantize")
+    L = load()
+    if x.dtype not in DT:
+        x = x.float()                      # the reference upcasts everything with .float()
+    if x.dim() == 0:
+        raise RuntimeError("mxfp4: cannot quantize a 0-d tensor")
+    cols = x.shape[-1]
+    lead = tuple(x.shape[:-1])
+    if x.dim() == 2 and x.stride(1) == 1 and x.stride(0) >= cols and x.numel() > 0:
+        ld = x.stride(0)                   # row-strided views go straight to the kernel
+    else:
+        x = x.contiguous()
+        ld = cols
+    rows = 1
+    for d in lead:
+        rows *= d
+    nblk = (cols + block_size - 1) // block_size
+    packed = torch.empty(lead + (nblk * block_size // 2,), dtype=torch.uint8, device=x.device)
+    scales = torch.empty(lead + (nblk,), dtype=torch.uint8 if scale_format == "e8m0" else torch.bfloat16, device=x.device)
+    with torch.cuda.device(x.device):
+        check(L.mxfp4_quantize(x.data_ptr(), DT[x.dtype], rows, cols, ld, block_size, SF[scale_format],
+                               packed.data_ptr(), scales.data_ptr(), stream_ptr(x.device)), "mxfp4_quantize")
+    return packed, scales
+
+
+def dequantize(packed: torch.Tensor, scales: torch.Tensor, block_size: int, out_dtype=torch.float32):
+    require_cuda(packed, "MXFP4Quantizer.dequantize")
+    L = load()
+    if packed.dtype != torch.uint8:
+        raise TypeError("mxfp4: packed data must be uint8")
+    if scales.dtype == torch.uint8:
+        fmt = "e8m0"
+    else:
+        fmt = "bf16"
+        if scales.dtype != torch.bfloat16:
+            # the reference applies scales.float(); only bf16 is produced by its quantiser, other float
+            # scales are rounded here if they are not already bf16 values
+            s16 = scales.to(torch.bfloat16)
+            if not torch.equal(s16.float(), scales.float()):
+                raise MXFP4BackendError("mxfp4: float scales must be representable in bfloat16")
+            scales = s16
+    packed = packed.contiguous()
+    scales = scales.to(packed.device).contiguous()
+    cols_pad = packed.shape[-1] * 2
+    rows = packed.numel() // packed.shape[-1] if packed.shape[-1] else 0
+    if scales.numel() * block_size != rows * cols_pad:
+        raise RuntimeError(f"mxfp4: shape mismatch: {scales.numel()} scales x block {block_size} != {rows * cols_pad} elements")
+    out = torch.empty(tuple(packed.shape[:-1]) + (cols_pad,), dtype=out_dtype, device=packed.device)
+    with torch.cuda.device(packed.device):
+        check(L.mxfp4_dequantize(packed.data_ptr(), scales.data_ptr(), SF[fmt], rows, cols_pad, block_size,
+                                 out.data_ptr(), DT[out_dtype], stream_ptr(packed.device)), "mxfp4_dequantize")
+    return out
