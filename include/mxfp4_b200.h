@@ -83,6 +83,60 @@ MXFP4_API int mxfp4_quantize(const void* x, int x_dtype, int64_t rows, int64_t c
 MXFP4_API int mxfp4_dequantize(const uint8_t* packed, const void* scales, int scale_fmt, int64_t rows, int64_t cols_pad,
                      int block_size, void* out, int out_dtype, void* stream);
 
+/* GEMM modes */
+#define MXFP4_GEMM_EXACT 0 /* weights decode exactly as the reference dequantises them (two MMAs per K step) */
+#define MXFP4_GEMM_FAST 1  /* single pass: weight codes 0 and 1 decode as hardware E2M1 (0, 0.5); NOT parity */
+
+/*
+ * Bytes of the tensor-core scale layouts ("blocked": tiles of 128 rows x 4 blocks, 512 bytes each,
+ * byte (r%32)*16 + (r/32)*4 + c; rows padded to 128, K padded to 256).
+ *   activation scales: ceil(M/128) * ceil(K/256) * 1024
+ *   prepared weight scales: ceil(N/128) * ceil(K/256) * 2048  (the scale bytes and a copy decremented by one)
+ */
+MXFP4_API int64_t mxfp4_act_scales_bytes(int64_t M, int64_t K);
+MXFP4_API int64_t mxfp4_prepared_scales_bytes(int64_t N, int64_t K);
+
+/*
+ * Activation quantiser of the GEMM (the job QuTLASSBackend.quantize hands to a third-party kernel,
+ * src/mxfp4/backends.py:162-183): bf16 [M, K] (row pitch ld elements, K % 32 == 0) ->
+ *   a_packed      device, [M, K/2] uint8: hardware E2M1 codes {0,.5,1,1.5,2,3,4,6}, round-to-nearest-even,
+ *                 even element in the high nibble (the reference's byte order)
+ *   a_sf_blocked  device, mxfp4_act_scales_bytes(M, K): E8M0 byte = exponent of 2^ceil(log2(amax/6)) per 32-block
+ * x must be 32-byte aligned and ld*2 a multiple of 32; a_packed 16-byte aligned.
+ */
+MXFP4_API int mxfp4_act_quantize(const void* x_bf16, int64_t M, int64_t K, int64_t ld, uint8_t* a_packed,
+                                 uint8_t* a_sf_blocked, void* stream);
+
+/*
+ * Re-tiles a weight's E8M0 scales [N, K/32] (as mxfp4_quantize / the reference produce them) into the
+ * tensor-core layout, mxfp4_prepared_scales_bytes(N, K) bytes.  Done once per weight; the result is a
+ * cache, not part of the checkpoint (the reference's to_blocked() call per matmul, src/mxfp4/backends.py:227-228).
+ */
+MXFP4_API int mxfp4_prepare_weight_scales(const uint8_t* scales, int64_t N, int64_t K, uint8_t* prepared, void* stream);
+
+/* Workspace of mxfp4_gemm: 256-byte status block + packed activations + blocked activation scales. */
+MXFP4_API int64_t mxfp4_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K, int mode);
+
+/*
+ * out[M,N] (bf16, row pitch ldo) = act_quantize(x)[M,K] . Wref[N,K]^T (+ bias[N], bf16), float32 accumulation on
+ * the block-scaled FP4 tensor cores.  Replaces quant_matmul / backend.matmul, src/mxfp4/kernel_dispatcher.py:163-198
+ * and src/mxfp4/backends.py:191-312.
+ *   x_bf16         device, [M, K] bf16, row pitch ldx elements
+ *   w_packed       device, [N, K/2] uint8, the reference's packed weight, unchanged
+ *   w_sf_prepared  device, from mxfp4_prepare_weight_scales
+ *   workspace      device, >= mxfp4_gemm_workspace_bytes, 256-byte aligned.  Its first int is a status word that the
+ *                  caller zeroes once; a kernel whose bounded wait ran out stores MXFP4_E_TIMEOUT there.
+ * K % 32 == 0.  Launches two kernels (activation quantiser, GEMM) on `stream`.
+ */
+MXFP4_API int mxfp4_gemm(const void* x_bf16, int64_t ldx, const uint8_t* w_packed, const uint8_t* w_sf_prepared,
+                         const void* bias_bf16, void* out_bf16, int64_t ldo, int64_t M, int64_t N, int64_t K, int mode,
+                         void* workspace, int64_t workspace_bytes, void* stream);
+
+/* The GEMM alone, on activations already quantised by mxfp4_act_quantize.  status_dev may be NULL. */
+MXFP4_API int mxfp4_gemm_prequantized(const uint8_t* a_packed, const uint8_t* a_sf_blocked, const uint8_t* w_packed,
+                                      const uint8_t* w_sf_prepared, const void* bias_bf16, void* out_bf16, int64_t ldo,
+                                      int64_t M, int64_t N, int64_t K, int mode, int* status_dev, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,0 +1,448 @@
+// quant_matmul on Blackwell's block-scaled FP4 tensor cores (sm_100a, tcgen05 / TMEM / TMA).
+//
+//   out[M,N] (bf16) = Xq[M,K] . Wref[N,K]^T (+ bias)
+//
+// Xq   : activations after mxfp4_act_quantize (hardware E2M1 codes, E8M0 scales);
+// Wref : the weight exactly as the reference dequantises it (src/mxfp4/quantizer.py:143-198), i.e.
+//        magnitudes {0.5,.75,1,1.5,2,3,4,6} * 2^(b-127).  Hardware E2M1 decodes codes 0 and 1 as 0 and
+//        0.5 instead of 0.5 and 0.75, so in EXACT mode every K step issues two MMAs into the same
+//        accumulator:   Wref = HW(codes) * 2^(b-127)  +  HW(corr) * 2^(b-128),
+//        corr = sign | (code==0 ? 2 : code==1 ? 1 : 0), built in shared memory by the transform warps
+//        from the tile TMA just delivered.  The reference bytes are consumed as they are (the "even
+//        element in the high nibble" order is shared by both operands, so dot products are unchanged).
+//        FAST mode skips the correction pass (weights then decode as hardware E2M1; not parity).
+//
+// Tiling: one CTA computes a 128 (weight rows, the MMA's M / TMEM lanes) x BN (activation rows, the
+// MMA's N / TMEM columns) tile of out^T.  K advances in stages of 256 elements (128 bytes per row,
+// one 128-byte swizzle span), 4 MMAs of K=64 per stage and pass.
+// Warps: 0 = TMA producer, 1 = MMA issuer (owns TMEM), 2..5 = correction transform, then epilogue.
+// Every wait is bounded; a wait that runs out records MXFP4_E_TIMEOUT in the status word and the
+// CTA drains and exits.
+#include <cuda.h>
+
+#include "mxfp4_common.cuh"
+
+namespace mxfp4 {
+namespace {
+
+constexpr int kTileW = 128;         // weight rows per CTA (MMA M)
+constexpr int kStageK = 256;        // elements of K per pipeline stage
+constexpr int kStageKBytes = 128;   // bytes per row per stage
+constexpr uint32_t kSpinLimit = 1u << 22;
+
+// ---------------------------------------------------------------- PTX wrappers
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait.  Returns false (and raises the CTA's abort flag) when the limit is reached or another
+// role has already given up.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+    for (uint32_t it = 0; it < kSpinLimit; ++it) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if (it > 32) {
+            __nanosleep(64);
+            if (*abort_flag) return false;
+        }
+    }
+    *abort_flag = 1;
+    return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(dst),
+                 "l"(map), "r"(bar), "r"(x), "r"(y)
+                 : "memory");
+}
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst), "l"(src), "r"(bytes),
+                 "r"(bar)
+                 : "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_cp_sf(uint32_t tmem_addr, uint64_t sdesc) {
+    asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(tmem_addr), "l"(sdesc) : "memory");
+}
+__device__ __forceinline__ void tc_mma_mxf4(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t sfa, uint32_t sfb,
+                                            uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::mxf4.block_scale.block32 [%0], %1, %2, %3, [%5], [%6], p;\n\t}" ::"r"(d_tmem),
+        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(sfa), "r"(sfb)
+        : "memory");
+}
+__device__ __forceinline__ void tc_ld_32x32(uint32_t taddr, uint32_t (&v)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,"
+        "%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]), "=r"(v[9]), "=r"(v[10]),
+          "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]),
+          "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]),
+          "=r"(v[31])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// Shared-memory matrix descriptor, K-major operand tile whose rows are 128 bytes, 128-byte swizzle:
+// 8-row groups 1024 bytes apart.  Fields: start>>4 [0,14) | LBO>>4 [16,30) | SBO>>4 [32,46) |
+// version=1 [46,48) | layout [61,64) with 2 = SWIZZLE_128B.
+__device__ __forceinline__ uint64_t desc_sw128(uint32_t saddr) {
+    return (uint64_t)((saddr & 0x3FFFFu) >> 4) | (1ull << 16) | ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
+}
+// Descriptor of one 512-byte scale tile (32 rows x 16 bytes, no swizzle, 8-row groups 128 bytes apart).
+__device__ __forceinline__ uint64_t desc_sf(uint32_t saddr) {
+    return (uint64_t)((saddr & 0x3FFFFu) >> 4) | ((uint64_t)(128 >> 4) << 32) | (1ull << 46);
+}
+// Instruction descriptor for kind::mxf4 (block-scaled): A/B format E2M1 (=1) at [7,10)/[10,13), both
+// K-major, N>>3 at [17,23), scale format UE8M0 (=1) at bit 23, M>>4 at [24,29), scale-factor byte
+// selectors for B at [4,6) and A at [29,31) (0 or 2: which half of the 4 scale bytes per row), K=64.
+__device__ __forceinline__ uint32_t make_idesc(int n, uint32_t sf_id) {
+    return (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | (1u << 23) | ((uint32_t)(kTileW >> 4) << 24) | (sf_id << 29) | (sf_id << 4);
+}
+
+// corr nibble = sign | (code==0 ? 2 : code==1 ? 1 : 0), eight nibbles at a time
+__device__ __forceinline__ uint32_t corr_word(uint32_t w) {
+    const uint32_t e0 = ~((w >> 2) | (w >> 1)) & 0x11111111u;      // bit 0 of each nibble: exponent field is zero
+    return (w & (e0 << 3)) | ((e0 & ~w) << 1) | (e0 & w);
+}
+
+template <int BN>
+struct Cfg {
+    static constexpr int kXT = (BN + 127) / 128;                   // 128-row groups of activation scales per tile
+    static constexpr int kWBytes = kTileW * kStageKBytes;          // 16 KB
+    static constexpr int kXBytes = BN * kStageKBytes;
+    static constexpr int kSfwBytes = 2048;
+    static constexpr int kSfxBytes = 1024 * kXT;
+    static constexpr int kOffC = kWBytes;
+    static constexpr int kOffX = 2 * kWBytes;
+    static constexpr int kOffSfw = kOffX + kXBytes;
+    static constexpr int kOffSfx = kOffSfw + kSfwBytes;
+    static constexpr int kStageBytes = (kOffSfx + kSfxBytes + 1023) / 1024 * 1024;
+    static constexpr int kStages = (224 * 1024 / kStageBytes) < 8 ? (224 * 1024 / kStageBytes) : 8;
+    static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
+    static constexpr uint32_t kTxBytes = kWBytes + kXBytes + kSfwBytes + kSfxBytes;
+    // tensor-memory columns: accumulator [0,BN), then scale factors
+    static constexpr int kColSfw = 256;            // 2 tiles x 4 columns (pass 1), +8 for pass 2
+    static constexpr int kColSfw2 = 264;
+    static constexpr int kColSfx = 272;            // 2 K-tiles x 4*kXT columns
+    static constexpr int kTmemCols = 512;
+};
+
+struct GemmParams {
+    const uint8_t* sfw;     // prepared weight scales
+    const uint8_t* sfx;     // blocked activation scales
+    const __nv_bfloat16* bias;
+    __nv_bfloat16* out;
+    int64_t ldo;
+    int M, N, K;
+    int kstages;            // ceil(K / 256)
+    int exact;
+    int* status;
+};
+
+template <int BN>
+__global__ void __launch_bounds__(192, 1) gemm_mxf4_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+                                                           const GemmParams p) {
+    using C = Cfg<BN>;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw = smem_u32(smem_raw);
+    const uint32_t base = (raw + 1023u) & ~1023u;                 // stages need 1024-byte alignment (128-byte swizzle)
+    uint8_t* base_ptr = smem_raw + (base - raw);
+    const uint32_t bars = base + C::kStages * C::kStageBytes;     // full[S], empty[S], corr[S], accum, then tmem slot + abort flag
+    auto full_bar = [&](int s) { return bars + 8u * s; };
+    auto empty_bar = [&](int s) { return bars + 8u * (C::kStages + s); };
+    auto corr_bar = [&](int s) { return bars + 8u * (2 * C::kStages + s); };
+    const uint32_t accum_bar = bars + 8u * (3 * C::kStages);
+    uint8_t* tail = base_ptr + C::kStages * C::kStageBytes + 8 * (3 * C::kStages + 1);
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(tail);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tail + 4);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n_tile = blockIdx.x, m_tile = blockIdx.y;
+    const int nks = p.kstages;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < C::kStages; ++s) {
+            mbar_init(full_bar(s), 1);
+            mbar_init(empty_bar(s), 1);
+            mbar_init(corr_bar(s), 4);
+        }
+        mbar_init(accum_bar, 1);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32((const void*)tmem_slot)), "r"(C::kTmemCols)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            for (int ks = 0; ks < nks; ++ks) {
+                const int s = ks % C::kStages;
+                const uint32_t ph = (ks / C::kStages) & 1;
+                if (!mbar_wait(empty_bar(s), ph ^ 1u, abort_flag)) break;
+                const uint32_t st = base + s * C::kStageBytes;
+                mbar_expect_tx(full_bar(s), C::kTxBytes);
+                tma_load_2d(st, &map_w, full_bar(s), ks * kStageKBytes, n_tile * kTileW);
+                tma_load_2d(st + C::kOffX, &map_x, full_bar(s), ks * kStageKBytes, m_tile * BN);
+                bulk_load(st + C::kOffSfw, p.sfw + ((int64_t)n_tile * nks + ks) * 2048, 2048, full_bar(s));
+#pragma unroll
+                for (int t = 0; t < C::kXT; ++t) {
+                    const int64_t grp = ((int64_t)m_tile * BN) / 128 + t;
+                    bulk_load(st + C::kOffSfx + t * 1024, p.sfx + (grp * nks + ks) * 1024, 1024, full_bar(s));
+                }
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            const uint32_t idesc0 = make_idesc(BN, 0), idesc2 = make_idesc(BN, 2);
+            // activation scales of a tile narrower than 128 rows sit in a column offset of their 128-row group
+            const uint32_t sfx_col = tmem + C::kColSfx + (BN < 128 ? ((m_tile * BN) % 128) / 32 : 0);
+            bool ok = true;
+            for (int ks = 0; ks < nks && ok; ++ks) {
+                const int s = ks % C::kStages;
+                const uint32_t ph = (ks / C::kStages) & 1;
+                ok = mbar_wait(full_bar(s), ph, abort_flag);
+                if (ok && p.exact) ok = mbar_wait(corr_bar(s), ph, abort_flag);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t st = base + s * C::kStageBytes;
+                // scale factors: shared memory -> tensor memory (in order with the MMAs on the tensor pipe)
+#pragma unroll
+                for (int g = 0; g < 2; ++g) {
+                    tc_cp_sf(tmem + C::kColSfw + 4 * g, desc_sf(st + C::kOffSfw + 512 * g));
+                    tc_cp_sf(tmem + C::kColSfw2 + 4 * g, desc_sf(st + C::kOffSfw + 1024 + 512 * g));
+#pragma unroll
+                    for (int t = 0; t < C::kXT; ++t)
+                        tc_cp_sf(tmem + C::kColSfx + 4 * C::kXT * g + 4 * t, desc_sf(st + C::kOffSfx + 1024 * t + 512 * g));
+                }
+                const uint64_t wdesc = desc_sw128(st), cdesc = desc_sw128(st + C::kOffC), xdesc = desc_sw128(st + C::kOffX);
+#pragma unroll
+                for (int kb = 0; kb < 4; ++kb) {
+                    const int g = kb >> 1;
+                    const uint32_t idesc = (kb & 1) ? idesc2 : idesc0;
+                    const uint64_t adv = (uint64_t)(kb * 32 >> 4);             // 64 elements = 32 bytes along K
+                    const uint32_t sfb = sfx_col + 4 * C::kXT * g;
+                    tc_mma_mxf4(tmem, wdesc + adv, xdesc + adv, idesc, tmem + C::kColSfw + 4 * g, sfb, (ks | kb) != 0);
+                    if (p.exact) tc_mma_mxf4(tmem, cdesc + adv, xdesc + adv, idesc, tmem + C::kColSfw2 + 4 * g, sfb, 1u);
+                }
+                tc_commit(empty_bar(s));      // frees the stage once these MMAs have read it
+            }
+            tc_commit(accum_bar);             // accumulator complete (or abandoned)
+        }
+        __syncwarp();
+    } else {
+        // ------------------------------------------------------------------ transform, then epilogue
+        const int t = threadIdx.x - 64;       // 0..127
+        bool ok = true;
+        if (p.exact) {
+            for (int ks = 0; ks < nks && ok; ++ks) {
+                const int s = ks % C::kStages;
+                const uint32_t ph = (ks / C::kStages) & 1;
+                ok = __all_sync(0xFFFFFFFFu, mbar_wait(full_bar(s), ph, abort_flag));   // warp-uniform decision
+                if (!ok) break;
+                const uint4* src = reinterpret_cast<const uint4*>(base_ptr + s * C::kStageBytes);
+                uint4* dst = reinterpret_cast<uint4*>(base_ptr + s * C::kStageBytes + C::kOffC);
+#pragma unroll
+                for (int i = 0; i < C::kWBytes / 16 / 128; ++i) {
+                    uint4 v = src[i * 128 + t];           // same offset in and out: the swizzle is preserved
+                    v.x = corr_word(v.x); v.y = corr_word(v.y); v.z = corr_word(v.z); v.w = corr_word(v.w);
+                    dst[i * 128 + t] = v;
+                }
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // make the writes visible to the tensor core
+                __syncwarp();
+                if (lane == 0) mbar_arrive(corr_bar(s));
+            }
+        }
+        if (ok) ok = mbar_wait(accum_bar, 0, abort_flag);
+        ok = __all_sync(0xFFFFFFFFu, ok && !*abort_flag);
+        if (ok) {
+            tc_fence_after();
+            const int q = warp & 3;                               // TMEM lane quarter this warp may read
+            const int n = n_tile * kTileW + q * 32 + lane;
+            const float bias = (p.bias != nullptr && n < p.N) ? __bfloat162float(p.bias[n]) : 0.0f;
+            const bool has_bias = p.bias != nullptr;
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += 32) {
+                const int m0 = m_tile * BN + c0;
+                if (m0 >= p.M) break;                             // uniform across the warp
+                uint32_t v[32];
+                tc_ld_32x32(tmem + ((uint32_t)(q * 32) << 16) + c0, v);
+                if (n < p.N) {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        if (m0 + j < p.M) {
+                            __nv_bfloat16 y = __float2bfloat16_rn(__uint_as_float(v[j]));
+                            if (has_bias) y = __float2bfloat16_rn(__bfloat162float(y) + bias);   // `output += bias` in bf16
+                            p.out[(int64_t)(m0 + j) * p.ldo + n] = y;
+                        }
+                    }
+                }
+            }
+        }
+    }
+
+    // ---------------------------------------------------------------------- teardown
+    tc_fence_before();
+    __syncthreads();
+    if (*abort_flag) {
+        if (threadIdx.x == 0) {
+            if (p.status) atomicExch(p.status, MXFP4_E_TIMEOUT);
+            for (int i = 0; i < 2000; ++i) __nanosleep(1000);     // let copies and MMAs in flight retire before freeing
+        }
+        __syncthreads();
+    }
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(C::kTmemCols) : "memory");
+    }
+}
+
+// ---------------------------------------------------------------- host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess && qres == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)ptr;
+    }
+    return fn;
+}
+
+// Byte matrix [rows, row_bytes] (row pitch = row_bytes), box = 128 bytes x box_rows, 128-byte swizzle,
+// out-of-range parts of a box read as zero.
+int make_map(CUtensorMap* map, const void* ptr, int64_t rows, int64_t row_bytes, int box_rows) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) { set_error("cuTensorMapEncodeTiled is not available from this driver"); return MXFP4_E_CUDA; }
+    cuuint64_t dims[2] = {(cuuint64_t)row_bytes, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)row_bytes};
+    cuuint32_t box[2] = {(cuuint32_t)kStageKBytes, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) { set_error("cuTensorMapEncodeTiled failed with CUresult %d (rows=%lld, row_bytes=%lld)", (int)r, (long long)rows, (long long)row_bytes); return MXFP4_E_CUDA; }
+    return MXFP4_OK;
+}
+
+template <int BN>
+int launch_gemm(const CUtensorMap& mw, const CUtensorMap& mx, const GemmParams& p, cudaStream_t st) {
+    using C = Cfg<BN>;
+    static bool configured[64] = {false};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !configured[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_mxf4_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
+        if (e != cudaSuccess) return cuda_fail(e, "mxfp4_gemm: cudaFuncSetAttribute");
+        configured[dev] = true;
+    }
+    dim3 grid((p.N + kTileW - 1) / kTileW, (p.M + BN - 1) / BN);
+    gemm_mxf4_kernel<BN><<<grid, 192, C::kSmemBytes, st>>>(mw, mx, p);
+    MXFP4_CHECK_LAUNCH("mxfp4_gemm (tcgen05 kernel)");
+    return MXFP4_OK;
+}
+
+inline int64_t align_up(int64_t v, int64_t a) { return (v + a - 1) / a * a; }
+
+}  // namespace
+}  // namespace mxfp4
+
+extern "C" int64_t mxfp4_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K, int mode) {
+    (void)N; (void)mode;
+    if (M <= 0 || K <= 0) return 0;
+    // [status word, 256 B] [packed activations M*K/2] [blocked activation scales]
+    return 256 + mxfp4::align_up(M * (K / 2), 256) + mxfp4_act_scales_bytes(M, K);
+}
+
+extern "C" int mxfp4_gemm_prequantized(const uint8_t* a_packed, const uint8_t* a_sf_blocked, const uint8_t* w_packed,
+                                       const uint8_t* w_sf_prepared, const void* bias_bf16, void* out_bf16, int64_t ldo, int64_t M,
+                                       int64_t N, int64_t K, int mode, int* status_dev, void* stream) {
+    using namespace mxfp4;
+    if (M < 0 || N < 0 || K < 0) { set_error("mxfp4_gemm: negative size"); return MXFP4_E_SHAPE; }
+    if (M == 0 || N == 0) return MXFP4_OK;
+    if (K == 0 || K % 32) { set_error("mxfp4_gemm: K=%lld must be a positive multiple of 32", (long long)K); return MXFP4_E_SHAPE; }
+    if (M > 0x7FFFFFFF || N > 0x7FFFFFFF || K > 0x7FFFFFFF) { set_error("mxfp4_gemm: dimension too large"); return MXFP4_E_SHAPE; }
+    if (!a_packed || !a_sf_blocked || !w_packed || !w_sf_prepared || !out_bf16) { set_error("mxfp4_gemm: null pointer"); return MXFP4_E_BADARG; }
+    if (mode != MXFP4_GEMM_EXACT && mode != MXFP4_GEMM_FAST) { set_error("mxfp4_gemm: unknown mode %d", mode); return MXFP4_E_BADARG; }
+    if (ldo < N) { set_error("mxfp4_gemm: ldo < N"); return MXFP4_E_SHAPE; }
+    if ((uintptr_t)a_packed % 16 || (uintptr_t)w_packed % 16 || (uintptr_t)a_sf_blocked % 16 || (uintptr_t)w_sf_prepared % 16) {
+        set_error("mxfp4_gemm: packed operands and scale buffers must be 16-byte aligned");
+        return MXFP4_E_ALIGN;
+    }
+    CUtensorMap mw, mx;
+    const int bn = M <= 32 ? 32 : (M <= 64 ? 64 : (M <= 128 ? 128 : 256));
+    int rc = make_map(&mw, w_packed, N, K / 2, kTileW);
+    if (rc) return rc;
+    rc = make_map(&mx, a_packed, M, K / 2, bn);
+    if (rc) return rc;
+    GemmParams p;
+    p.sfw = w_sf_prepared; p.sfx = a_sf_blocked; p.bias = (const __nv_bfloat16*)bias_bf16; p.out = (__nv_bfloat16*)out_bf16;
+    p.ldo = ldo; p.M = (int)M; p.N = (int)N; p.K = (int)K; p.kstages = (int)((K + kStageK - 1) / kStageK);
+    p.exact = mode == MXFP4_GEMM_EXACT; p.status = status_dev;
+    cudaStream_t st = (cudaStream_t)stream;
+    switch (bn) {
+        case 32: return launch_gemm<32>(mw, mx, p, st);
+        case 64: return launch_gemm<64>(mw, mx, p, st);
+        case 128: return launch_gemm<128>(mw, mx, p, st);
+        default: return launch_gemm<256>(mw, mx, p, st);
+    }
+}
+
+extern "C" int mxfp4_gemm(const void* x_bf16, int64_t ldx, const uint8_t* w_packed, const uint8_t* w_sf_prepared, const void* bias_bf16,
+                          void* out_bf16, int64_t ldo, int64_t M, int64_t N, int64_t K, int mode, void* workspace,
+                          int64_t workspace_bytes, void* stream) {
+    using namespace mxfp4;
+    if (M < 0 || N < 0 || K < 0) { set_error("mxfp4_gemm: negative size"); return MXFP4_E_SHAPE; }
+    if (M == 0 || N == 0) return MXFP4_OK;
+    if (K == 0 || K % 32) { set_error("mxfp4_gemm: K=%lld must be a positive multiple of 32", (long long)K); return MXFP4_E_SHAPE; }
+    if (!x_bf16 || !workspace) { set_error("mxfp4_gemm: null pointer"); return MXFP4_E_BADARG; }
+    if (workspace_bytes < mxfp4_gemm_workspace_bytes(M, N, K, mode)) {
+        set_error("mxfp4_gemm: workspace of %lld bytes, need %lld", (long long)workspace_bytes, (long long)mxfp4_gemm_workspace_bytes(M, N, K, mode));
+        return MXFP4_E_WORKSPACE;
+    }
+    if ((uintptr_t)workspace % 256) { set_error("mxfp4_gemm: workspace must be 256-byte aligned"); return MXFP4_E_ALIGN; }
+    uint8_t* ws = (uint8_t*)workspace;
+    int* status = (int*)ws;
+    uint8_t* a_packed = ws + 256;
+    uint8_t* a_sf = a_packed + align_up(M * (K / 2), 256);
+    int rc = mxfp4_act_quantize(x_bf16, M, K, ldx, a_packed, a_sf, stream);
+    if (rc) return rc;
+    return mxfp4_gemm_prequantized(a_packed, a_sf, w_packed, w_sf_prepared, bias_bf16, out_bf16, ldo, M, N, K, mode, status, stream);
+}

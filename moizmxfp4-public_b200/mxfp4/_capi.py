@@ -44,17 +44,20 @@ def load():
     L.mxfp4_dequantize.argtypes = [vp, vp, ci, i64, i64, ci, vp, ci, vp]
     for name in ("mxfp4_device_info", "mxfp4_quantize", "mxfp4_dequantize"):
         getattr(L, name).restype = ci
-    if hasattr(L, "mxfp4_gemm"):
-        L.mxfp4_act_quantize.argtypes = [vp, i64, i64, i64, vp, vp, vp]
-        L.mxfp4_act_quantize.restype = ci
-        L.mxfp4_prepare_weight_scales.argtypes = [vp, i64, i64, vp, vp]
-        L.mxfp4_prepare_weight_scales.restype = ci
-        L.mxfp4_prepared_scales_bytes.argtypes = [i64, i64]
-        L.mxfp4_prepared_scales_bytes.restype = i64
-        L.mxfp4_gemm_workspace_bytes.argtypes = [i64, i64, i64, ci]
-        L.mxfp4_gemm_workspace_bytes.restype = i64
-        L.mxfp4_gemm.argtypes = [vp, i64, vp, vp, vp, vp, i64, i64, i64, i64, ci, vp, i64, vp, vp]
-        L.mxfp4_gemm.restype = ci
+    L.mxfp4_act_scales_bytes.argtypes = [i64, i64]
+    L.mxfp4_act_scales_bytes.restype = i64
+    L.mxfp4_prepared_scales_bytes.argtypes = [i64, i64]
+    L.mxfp4_prepared_scales_bytes.restype = i64
+    L.mxfp4_act_quantize.argtypes = [vp, i64, i64, i64, vp, vp, vp]
+    L.mxfp4_act_quantize.restype = ci
+    L.mxfp4_prepare_weight_scales.argtypes = [vp, i64, i64, vp, vp]
+    L.mxfp4_prepare_weight_scales.restype = ci
+    L.mxfp4_gemm_workspace_bytes.argtypes = [i64, i64, i64, ci]
+    L.mxfp4_gemm_workspace_bytes.restype = i64
+    L.mxfp4_gemm.argtypes = [vp, i64, vp, vp, vp, vp, i64, i64, i64, i64, ci, vp, i64, vp]
+    L.mxfp4_gemm.restype = ci
+    L.mxfp4_gemm_prequantized.argtypes = [vp, vp, vp, vp, vp, vp, i64, i64, i64, i64, ci, vp, vp]
+    L.mxfp4_gemm_prequantized.restype = ci
     _lib = L
     return L
 

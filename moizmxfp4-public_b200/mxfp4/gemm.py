@@ -1,0 +1,155 @@
+"""Host side of quant_matmul / MXLinear.forward: operand preparation caches, workspace, launch.
+
+The arithmetic is entirely in libmxfp4_b200.so (mxfp4_act_quantize + the tcgen05 GEMM kernel).  This
+module only keeps, per weight, the scale bytes re-tiled for the tensor cores (a cache rebuilt on
+demand, never part of a checkpoint) and, per device and stream, a workspace for the quantised
+activations.
+"""
+import os
+import threading
+from collections import OrderedDict
+from typing import Optional
+
+import torch
+
+from . import _capi
+
+_MODES = {"exact": _capi.GEMM_EXACT, "fast": _capi.GEMM_FAST}
+_mode = _MODES[os.environ.get("MXFP4_GEMM_MODE", "exact")]
+_lock = threading.Lock()
+_prepared = OrderedDict()        # (ptr, numel, device index, version) -> prepared scale tensor
+_PREPARED_MAX = 4096
+_workspaces = {}                 # (device index, stream) -> uint8 tensor
+
+
+def set_gemm_mode(mode: str):
+    """"exact" (default): weights decode exactly as the reference dequantises them, two MMAs per K step.
+    "fast": single pass with hardware E2M1 decoding of the weight codes; faster, not parity."""
+    global _mode
+    _mode = _MODES[mode]
+
+
+def get_gemm_mode() -> str:
+    return "exact" if _mode == _capi.GEMM_EXACT else "fast"
+
+
+def prepared_scales(weight_scales: torch.Tensor, N: int, K: int) -> torch.Tensor:
+    """Tensor-core layout of a weight's E8M0 scales, cached by storage identity and version counter
+    (an in-place update such as load_state_dict bumps the version and invalidates the entry)."""
+    key = (weight_scales.data_ptr(), weight_scales.numel(), weight_scales.device.index, weight_scales._version)
+    with _lock:
+        hit = _prepared.get(key)
+        if hit is not None:
+            _prepared.move_to_end(key)
+            return hit
+    L = _capi.load()
+    ws = weight_scales.contiguous()
+    out = torch.empty(L.mxfp4_prepared_scales_bytes(N, K), dtype=torch.uint8, device=ws.device)
+    with torch.cuda.device(ws.device):
+        _capi.check(L.mxfp4_prepare_weight_scales(ws.data_ptr(), N, K, out.data_ptr(), _capi.stream_ptr(ws.device)),
+                    "mxfp4_prepare_weight_scales")
+    with _lock:
+        _prepared[key] = out
+        while len(_prepared) > _PREPARED_MAX:
+            _prepared.popitem(last=False)
+    return out
+
+
+def _workspace(device: torch.device, nbytes: int) -> torch.Tensor:
+    key = (device.index, torch.cuda.current_stream(device).cuda_stream)
+    ws = _workspaces.get(key)
+    if ws is None or ws.numel() < nbytes:
+        ws = torch.zeros(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)   # zeroed: the status word starts clear
+        _workspaces[key] = ws
+    return ws
+
+
+def check_status(device=None):
+    """Synchronises and raises if a GEMM kernel on `device` reported a bounded wait that ran out."""
+    for (idx, _), ws in list(_workspaces.items()):
+        if device is not None and torch.device(device).index not in (None, idx):
+            continue
+        code = int(ws[:4].view(torch.int32).item())
+        if code != 0:
+            ws[:4].zero_()
+            raise _capi.MXFP4BackendError(f"mxfp4 GEMM kernel reported status {code} (a device-side wait timed out)")
+
+
+def act_quantize(x: torch.Tensor):
+    """bf16 [M, K] -> (packed u8 [M, K/2], blocked E8M0 scales u8 [bytes]); the GEMM's own activation format."""
+    _capi.require_cuda(x, "act_quantize")
+    L = _capi.load()
+    assert x.dim() == 2 and x.dtype == torch.bfloat16
+    x = x.contiguous()
+    M, K = x.shape
+    packed = torch.empty(M, K // 2, dtype=torch.uint8, device=x.device)
+    sf = torch.empty(L.mxfp4_act_scales_bytes(M, K), dtype=torch.uint8, device=x.device)
+    with torch.cuda.device(x.device):
+        _capi.check(L.mxfp4_act_quantize(x.data_ptr(), M, K, K, packed.data_ptr(), sf.data_ptr(), _capi.stream_ptr(x.device)),
+                    "mxfp4_act_quantize")
+    return packed, sf
+
+
+def quant_matmul_2d(input: torch.Tensor, packed_weight: torch.Tensor, weight_scales: torch.Tensor,
+                    bias: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """[M,K] x packed [N,K/2] (+bias) -> [M,N]; argument contract of the reference's quant_matmul
+    (src/mxfp4/fused_kernels.py:160-207: 2-D tensors, K_packed*2 == K)."""
+    assert input.dim() == 2, "Input must be 2D [M, K]"
+    assert packed_weight.dim() == 2, "Packed weight must be 2D [N, K//2]"
+    M, K = input.shape
+    N, K_packed = packed_weight.shape
+    assert K_packed * 2 == K, f"Weight K dimension mismatch: {K_packed * 2} vs {K}"
+    _capi.require_cuda(input, "quant_matmul")
+    _capi.require_cuda(packed_weight, "quant_matmul")
+    if packed_weight.dtype != torch.uint8:
+        raise TypeError("mxfp4: packed_weight must be uint8")
+    if weight_scales.dtype != torch.uint8:
+        return _matmul_bf16_scales(input, packed_weight, weight_scales, bias)
+    if K % 32 != 0:
+        raise _capi.MXFP4BackendError(f"mxfp4: K={K} must be a multiple of 32 (pad activations to the packed weight's width)")
+    in_dtype = input.dtype
+    x = input if in_dtype == torch.bfloat16 else input.to(torch.bfloat16)
+    if x.stride(1) != 1 or (x.stride(0) * 2) % 32 != 0 or x.data_ptr() % 32 != 0:
+        x = x.contiguous()
+    L = _capi.load()
+    dev = x.device
+    pw = packed_weight.contiguous()
+    sfw = prepared_scales(weight_scales, N, K)
+    b = None
+    if bias is not None:
+        b = bias.to(device=dev, dtype=torch.bfloat16).contiguous()
+    if out is None:
+        out = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
+    if M == 0 or N == 0:
+        return out.to(in_dtype)
+    nbytes = L.mxfp4_gemm_workspace_bytes(M, N, K, _mode)
+    ws = _workspace(dev, nbytes)
+    with torch.cuda.device(dev):
+        _capi.check(L.mxfp4_gemm(x.data_ptr(), x.stride(0), pw.data_ptr(), sfw.data_ptr(), None if b is None else b.data_ptr(),
+                                 out.data_ptr(), out.stride(0), M, N, K, _mode, ws.data_ptr(), ws.numel(), _capi.stream_ptr(dev)),
+                    "mxfp4_gemm")
+    return out if in_dtype == torch.bfloat16 else out.to(in_dtype)
+
+
+def _matmul_bf16_scales(input, packed_weight, weight_scales, bias):
+    """scale_format="bf16" weights have no power-of-two scales, so they cannot feed the block-scaled
+    tensor-core path; they take the reference's own formulation (dequantise, cast, dense matmul,
+    src/mxfp4/backends.py:295-312) with this package's dequantiser."""
+    w = _capi.dequantize(packed_weight, weight_scales, 32, torch.float32).to(input.dtype)
+    out = torch.matmul(input, w.T)
+    if bias is not None:
+        out += bias
+    return out
+
+
+def mxlinear_forward(input: torch.Tensor, packed_weight: torch.Tensor, weight_scales: torch.Tensor,
+                     bias: Optional[torch.Tensor], in_features: int) -> torch.Tensor:
+    """MXLinear.forward for a quantised layer: any leading dimensions, output in the input's dtype."""
+    lead = input.shape[:-1]
+    x = input.reshape(-1, input.shape[-1])
+    k_pad = packed_weight.shape[-1] * 2
+    if x.shape[-1] != k_pad:
+        # the quantiser padded the weight rows to a multiple of the block; padded weight columns meet zeros
+        x = torch.nn.functional.pad(x, (0, k_pad - x.shape[-1]))
+    y = quant_matmul_2d(x, packed_weight, weight_scales, bias)
+    return y.reshape(*lead, packed_weight.shape[0])
