@@ -114,8 +114,11 @@ MXFP4_API int mxfp4_act_quantize(const void* x_bf16, int64_t M, int64_t K, int64
  */
 MXFP4_API int mxfp4_prepare_weight_scales(const uint8_t* scales, int64_t N, int64_t K, uint8_t* prepared, void* stream);
 
-/* Workspace of mxfp4_gemm: 256-byte status block + packed activations + blocked activation scales. */
+/* Workspace of mxfp4_gemm: 256-byte status block + packed activations + blocked activation scales + the
+ * float32 partial sums of a K-split (mxfp4_gemm_splitk_bytes; skinny problems, M <= 128, are cut along K so that
+ * every SM streams part of the weight; the partials are summed in a fixed order by a second kernel). */
 MXFP4_API int64_t mxfp4_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K, int mode);
+MXFP4_API int64_t mxfp4_gemm_splitk_bytes(int64_t M, int64_t N, int64_t K);
 
 /*
  * out[M,N] (bf16, row pitch ldo) = act_quantize(x)[M,K] . Wref[N,K]^T (+ bias[N], bf16), float32 accumulation on
@@ -132,10 +135,12 @@ MXFP4_API int mxfp4_gemm(const void* x_bf16, int64_t ldx, const uint8_t* w_packe
                          const void* bias_bf16, void* out_bf16, int64_t ldo, int64_t M, int64_t N, int64_t K, int mode,
                          void* workspace, int64_t workspace_bytes, void* stream);
 
-/* The GEMM alone, on activations already quantised by mxfp4_act_quantize.  status_dev may be NULL. */
+/* The GEMM alone, on activations already quantised by mxfp4_act_quantize.  splitk_workspace (16-byte aligned,
+ * >= mxfp4_gemm_splitk_bytes) may be NULL: the K-split is then not used.  status_dev may be NULL. */
 MXFP4_API int mxfp4_gemm_prequantized(const uint8_t* a_packed, const uint8_t* a_sf_blocked, const uint8_t* w_packed,
                                       const uint8_t* w_sf_prepared, const void* bias_bf16, void* out_bf16, int64_t ldo,
-                                      int64_t M, int64_t N, int64_t K, int mode, int* status_dev, void* stream);
+                                      int64_t M, int64_t N, int64_t K, int mode, void* splitk_workspace,
+                                      int64_t splitk_bytes, int* status_dev, void* stream);
 
 #ifdef __cplusplus
 }

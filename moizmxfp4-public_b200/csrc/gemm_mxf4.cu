@@ -132,7 +132,7 @@ __device__ __forceinline__ uint32_t corr_word(uint32_t w) {
 
 template <int BN>
 struct Cfg {
-    static constexpr int kXT = (BN + 127) / 128;                   // 128-row groups of activation scales per tile
+    static constexpr int kXT = BN <= 128 ? 1 : 2;                  // 128-row groups of activation scales a tile can touch
     static constexpr int kWBytes = kTileW * kStageKBytes;          // 16 KB
     static constexpr int kXBytes = BN * kStageKBytes;
     static constexpr int kSfwBytes = 2048;
@@ -142,48 +142,77 @@ struct Cfg {
     static constexpr int kOffSfw = kOffX + kXBytes;
     static constexpr int kOffSfx = kOffSfw + kSfwBytes;
     static constexpr int kStageBytes = (kOffSfx + kSfxBytes + 1023) / 1024 * 1024;
-    static constexpr int kStages = (224 * 1024 / kStageBytes) < 8 ? (224 * 1024 / kStageBytes) : 8;
-    static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
+    static constexpr int kEpiBytes = 4 * 4096;                     // per epilogue warp: 32 x 32 words for the transpose
+    static constexpr int kBudget = 227 * 1024 - 1024 /*alignment*/ - 512 /*barriers*/ - kEpiBytes;
+    static constexpr int kStages = (kBudget / kStageBytes) < 8 ? (kBudget / kStageBytes) : 8;
+    static constexpr int kSmemBytes = kStages * kStageBytes + kEpiBytes + 1024 + 512;
     static constexpr uint32_t kTxBytes = kWBytes + kXBytes + kSfwBytes + kSfxBytes;
-    // tensor-memory columns: accumulator [0,BN), then scale factors
-    static constexpr int kColSfw = 256;            // 2 tiles x 4 columns (pass 1), +8 for pass 2
-    static constexpr int kColSfw2 = 264;
-    static constexpr int kColSfx = 272;            // 2 K-tiles x 4*kXT columns
+    // tensor-memory columns: two accumulators, then scale factors
+    static constexpr int kAccStride = BN <= 128 ? 128 : 192;
+    static constexpr int kColSf = 2 * kAccStride;
+    static constexpr int kColSfw = kColSf;         // 2 K-tiles x 4 columns (pass 1)
+    static constexpr int kColSfw2 = kColSf + 8;    // same for pass 2
+    static constexpr int kColSfx = kColSf + 16;    // 2 K-tiles x 4*kXT columns
     static constexpr int kTmemCols = 512;
+    static_assert(BN % 32 == 0 && BN <= 192, "tile width");
+    static_assert(kColSfx + 8 * kXT <= 512, "tensor memory budget");
+    static_assert(kStages >= 2, "pipeline depth");
 };
 
 struct GemmParams {
     const uint8_t* sfw;     // prepared weight scales
     const uint8_t* sfx;     // blocked activation scales
     const __nv_bfloat16* bias;
-    __nv_bfloat16* out;
+    __nv_bfloat16* out;     // [M, ldo] bf16 (ksplit == 1)
+    float* partial;         // [ksplit, M, N] float32 (ksplit > 1)
     int64_t ldo;
     int M, N, K;
     int kstages;            // ceil(K / 256)
+    int ksplit;             // K is cut into this many ranges of whole stages, one work unit each
+    int n_tiles, m_tiles;
     int exact;
     int* status;
 };
 
+constexpr int kThreads = 320;   // warps: 0 producer, 1 MMA, 2-5 transform, 6-9 epilogue
+
+// A work unit is (k-range, weight tile, activation tile); units are dealt round-robin to the CTAs of
+// a persistent grid.  All roles walk the same unit sequence.
+struct Unit {
+    int n_tile, m_tile, ksp, ks0, ks1;
+};
+__device__ __forceinline__ Unit get_unit(const GemmParams& p, int u) {
+    Unit w;
+    w.ksp = u % p.ksplit;
+    const int t = u / p.ksplit;
+    w.n_tile = t % p.n_tiles;
+    w.m_tile = t / p.n_tiles;
+    w.ks0 = (int)((int64_t)p.kstages * w.ksp / p.ksplit);
+    w.ks1 = (int)((int64_t)p.kstages * (w.ksp + 1) / p.ksplit);
+    return w;
+}
+
 template <int BN>
-__global__ void __launch_bounds__(192, 1) gemm_mxf4_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
-                                                           const GemmParams p) {
+__global__ void __launch_bounds__(kThreads, 1) gemm_mxf4_kernel(const __grid_constant__ CUtensorMap map_w,
+                                                                const __grid_constant__ CUtensorMap map_x, const GemmParams p) {
     using C = Cfg<BN>;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;                 // stages need 1024-byte alignment (128-byte swizzle)
     uint8_t* base_ptr = smem_raw + (base - raw);
-    const uint32_t bars = base + C::kStages * C::kStageBytes;     // full[S], empty[S], corr[S], accum, then tmem slot + abort flag
+    uint8_t* epi_ptr = base_ptr + C::kStages * C::kStageBytes;
+    const uint32_t bars = base + C::kStages * C::kStageBytes + C::kEpiBytes;
     auto full_bar = [&](int s) { return bars + 8u * s; };
     auto empty_bar = [&](int s) { return bars + 8u * (C::kStages + s); };
     auto corr_bar = [&](int s) { return bars + 8u * (2 * C::kStages + s); };
-    const uint32_t accum_bar = bars + 8u * (3 * C::kStages);
-    uint8_t* tail = base_ptr + C::kStages * C::kStageBytes + 8 * (3 * C::kStages + 1);
+    auto acc_full_bar = [&](int b) { return bars + 8u * (3 * C::kStages + b); };
+    auto acc_empty_bar = [&](int b) { return bars + 8u * (3 * C::kStages + 2 + b); };
+    uint8_t* tail = epi_ptr + C::kEpiBytes + 8 * (3 * C::kStages + 4);
     volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(tail);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tail + 4);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int n_tile = blockIdx.x, m_tile = blockIdx.y;
-    const int nks = p.kstages;
+    const int total_units = p.n_tiles * p.m_tiles * p.ksplit;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < C::kStages; ++s) {
@@ -191,7 +220,10 @@ __global__ void __launch_bounds__(192, 1) gemm_mxf4_kernel(const __grid_constant
             mbar_init(empty_bar(s), 1);
             mbar_init(corr_bar(s), 4);
         }
-        mbar_init(accum_bar, 1);
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(acc_full_bar(b), 1);
+            mbar_init(acc_empty_bar(b), 4);
+        }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -209,19 +241,28 @@ __global__ void __launch_bounds__(192, 1) gemm_mxf4_kernel(const __grid_constant
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer
         if (lane == 0) {
-            for (int ks = 0; ks < nks; ++ks) {
-                const int s = ks % C::kStages;
-                const uint32_t ph = (ks / C::kStages) & 1;
-                if (!mbar_wait(empty_bar(s), ph ^ 1u, abort_flag)) break;
-                const uint32_t st = base + s * C::kStageBytes;
-                mbar_expect_tx(full_bar(s), C::kTxBytes);
-                tma_load_2d(st, &map_w, full_bar(s), ks * kStageKBytes, n_tile * kTileW);
-                tma_load_2d(st + C::kOffX, &map_x, full_bar(s), ks * kStageKBytes, m_tile * BN);
-                bulk_load(st + C::kOffSfw, p.sfw + ((int64_t)n_tile * nks + ks) * 2048, 2048, full_bar(s));
+            uint32_t it = 0;          // running stage counter across units
+            bool ok = true;
+            for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x) {
+                const Unit w = get_unit(p, u);
+                const int m0 = w.m_tile * BN;
+                for (int ks = w.ks0; ks < w.ks1; ++ks, ++it) {
+                    const int s = it % C::kStages;
+                    const uint32_t ph = (it / C::kStages) & 1;
+                    if (!mbar_wait(empty_bar(s), ph ^ 1u, abort_flag)) { ok = false; break; }
+                    const uint32_t st = base + s * C::kStageBytes;
+                    mbar_expect_tx(full_bar(s), C::kTxBytes);
+                    tma_load_2d(st, &map_w, full_bar(s), ks * kStageKBytes, w.n_tile * kTileW);
+                    tma_load_2d(st + C::kOffX, &map_x, full_bar(s), ks * kStageKBytes, m0);
+                    bulk_load(st + C::kOffSfw, p.sfw + ((int64_t)w.n_tile * p.kstages + ks) * 2048, 2048, full_bar(s));
 #pragma unroll
-                for (int t = 0; t < C::kXT; ++t) {
-                    const int64_t grp = ((int64_t)m_tile * BN) / 128 + t;
-                    bulk_load(st + C::kOffSfx + t * 1024, p.sfx + (grp * nks + ks) * 1024, 1024, full_bar(s));
+                    for (int t = 0; t < C::kXT; ++t) {
+                        // 128-row scale groups the tile touches; a second group past the end of the buffer is
+                        // replaced by the first (its rows are beyond M and never stored)
+                        int64_t grp = m0 / 128 + t;
+                        if (grp * 128 >= ((int64_t)p.M + 127) / 128 * 128) grp = m0 / 128;
+                        bulk_load(st + C::kOffSfx + t * 1024, p.sfx + (grp * p.kstages + ks) * 1024, 1024, full_bar(s));
+                    }
                 }
             }
         }
@@ -230,87 +271,158 @@ __global__ void __launch_bounds__(192, 1) gemm_mxf4_kernel(const __grid_constant
         // ------------------------------------------------------------------ MMA issuer
         if (lane == 0) {
             const uint32_t idesc0 = make_idesc(BN, 0), idesc2 = make_idesc(BN, 2);
-            // activation scales of a tile narrower than 128 rows sit in a column offset of their 128-row group
-            const uint32_t sfx_col = tmem + C::kColSfx + (BN < 128 ? ((m_tile * BN) % 128) / 32 : 0);
+            uint32_t it = 0;
+            int i = 0;                // units done by this CTA
             bool ok = true;
-            for (int ks = 0; ks < nks && ok; ++ks) {
-                const int s = ks % C::kStages;
-                const uint32_t ph = (ks / C::kStages) & 1;
-                ok = mbar_wait(full_bar(s), ph, abort_flag);
-                if (ok && p.exact) ok = mbar_wait(corr_bar(s), ph, abort_flag);
+            for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x, ++i) {
+                const Unit w = get_unit(p, u);
+                const int buf = i & 1;
+                const uint32_t acc = tmem + buf * C::kAccStride;
+                // activation scales of a tile that starts inside a 128-row group sit at a column offset
+                const uint32_t sfx_col = tmem + C::kColSfx + ((w.m_tile * BN) % 128) / 32;
+                ok = mbar_wait(acc_empty_bar(buf), ((i >> 1) & 1) ^ 1u, abort_flag);   // epilogue has drained this buffer
                 if (!ok) break;
                 tc_fence_after();
-                const uint32_t st = base + s * C::kStageBytes;
-                // scale factors: shared memory -> tensor memory (in order with the MMAs on the tensor pipe)
+                for (int ks = w.ks0; ks < w.ks1; ++ks, ++it) {
+                    const int s = it % C::kStages;
+                    const uint32_t ph = (it / C::kStages) & 1;
+                    ok = mbar_wait(full_bar(s), ph, abort_flag);
+                    if (ok && p.exact) ok = mbar_wait(corr_bar(s), ph, abort_flag);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint32_t st = base + s * C::kStageBytes;
+                    // scale factors: shared memory -> tensor memory (in order with the MMAs on the tensor pipe)
 #pragma unroll
-                for (int g = 0; g < 2; ++g) {
-                    tc_cp_sf(tmem + C::kColSfw + 4 * g, desc_sf(st + C::kOffSfw + 512 * g));
-                    tc_cp_sf(tmem + C::kColSfw2 + 4 * g, desc_sf(st + C::kOffSfw + 1024 + 512 * g));
+                    for (int g = 0; g < 2; ++g) {
+                        tc_cp_sf(tmem + C::kColSfw + 4 * g, desc_sf(st + C::kOffSfw + 512 * g));
+                        if (p.exact) tc_cp_sf(tmem + C::kColSfw2 + 4 * g, desc_sf(st + C::kOffSfw + 1024 + 512 * g));
 #pragma unroll
-                    for (int t = 0; t < C::kXT; ++t)
-                        tc_cp_sf(tmem + C::kColSfx + 4 * C::kXT * g + 4 * t, desc_sf(st + C::kOffSfx + 1024 * t + 512 * g));
+                        for (int t = 0; t < C::kXT; ++t)
+                            tc_cp_sf(tmem + C::kColSfx + 4 * C::kXT * g + 4 * t, desc_sf(st + C::kOffSfx + 1024 * t + 512 * g));
+                    }
+                    const uint64_t wdesc = desc_sw128(st), cdesc = desc_sw128(st + C::kOffC), xdesc = desc_sw128(st + C::kOffX);
+#pragma unroll
+                    for (int kb = 0; kb < 4; ++kb) {
+                        const int g = kb >> 1;
+                        const uint32_t idesc = (kb & 1) ? idesc2 : idesc0;
+                        const uint64_t adv = (uint64_t)(kb * 32 >> 4);             // 64 elements = 32 bytes along K
+                        const uint32_t sfb = sfx_col + 4 * C::kXT * g;
+                        tc_mma_mxf4(acc, wdesc + adv, xdesc + adv, idesc, tmem + C::kColSfw + 4 * g, sfb, (ks > w.ks0 || kb > 0) ? 1u : 0u);
+                        if (p.exact) tc_mma_mxf4(acc, cdesc + adv, xdesc + adv, idesc, tmem + C::kColSfw2 + 4 * g, sfb, 1u);
+                    }
+                    tc_commit(empty_bar(s));      // frees the stage once these MMAs have read it
                 }
-                const uint64_t wdesc = desc_sw128(st), cdesc = desc_sw128(st + C::kOffC), xdesc = desc_sw128(st + C::kOffX);
-#pragma unroll
-                for (int kb = 0; kb < 4; ++kb) {
-                    const int g = kb >> 1;
-                    const uint32_t idesc = (kb & 1) ? idesc2 : idesc0;
-                    const uint64_t adv = (uint64_t)(kb * 32 >> 4);             // 64 elements = 32 bytes along K
-                    const uint32_t sfb = sfx_col + 4 * C::kXT * g;
-                    tc_mma_mxf4(tmem, wdesc + adv, xdesc + adv, idesc, tmem + C::kColSfw + 4 * g, sfb, (ks | kb) != 0);
-                    if (p.exact) tc_mma_mxf4(tmem, cdesc + adv, xdesc + adv, idesc, tmem + C::kColSfw2 + 4 * g, sfb, 1u);
-                }
-                tc_commit(empty_bar(s));      // frees the stage once these MMAs have read it
+                tc_commit(acc_full_bar(buf));     // accumulator of this unit complete (or abandoned)
             }
-            tc_commit(accum_bar);             // accumulator complete (or abandoned)
         }
         __syncwarp();
-    } else {
-        // ------------------------------------------------------------------ transform, then epilogue
-        const int t = threadIdx.x - 64;       // 0..127
-        bool ok = true;
+    } else if (warp < 6) {
+        // ------------------------------------------------------------------ correction transform (EXACT mode)
         if (p.exact) {
-            for (int ks = 0; ks < nks && ok; ++ks) {
-                const int s = ks % C::kStages;
-                const uint32_t ph = (ks / C::kStages) & 1;
-                ok = __all_sync(0xFFFFFFFFu, mbar_wait(full_bar(s), ph, abort_flag));   // warp-uniform decision
-                if (!ok) break;
-                const uint4* src = reinterpret_cast<const uint4*>(base_ptr + s * C::kStageBytes);
-                uint4* dst = reinterpret_cast<uint4*>(base_ptr + s * C::kStageBytes + C::kOffC);
+            const int t = threadIdx.x - 64;       // 0..127
+            uint32_t it = 0;
+            bool ok = true;
+            for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x) {
+                const Unit w = get_unit(p, u);
+                for (int ks = w.ks0; ks < w.ks1; ++ks, ++it) {
+                    const int s = it % C::kStages;
+                    const uint32_t ph = (it / C::kStages) & 1;
+                    ok = __all_sync(0xFFFFFFFFu, mbar_wait(full_bar(s), ph, abort_flag));   // warp-uniform decision
+                    if (!ok) break;
+                    const uint4* src = reinterpret_cast<const uint4*>(base_ptr + s * C::kStageBytes);
+                    uint4* dst = reinterpret_cast<uint4*>(base_ptr + s * C::kStageBytes + C::kOffC);
 #pragma unroll
-                for (int i = 0; i < C::kWBytes / 16 / 128; ++i) {
-                    uint4 v = src[i * 128 + t];           // same offset in and out: the swizzle is preserved
-                    v.x = corr_word(v.x); v.y = corr_word(v.y); v.z = corr_word(v.z); v.w = corr_word(v.w);
-                    dst[i * 128 + t] = v;
+                    for (int j = 0; j < C::kWBytes / 16 / 128; ++j) {
+                        uint4 v = src[j * 128 + t];           // same offset in and out: the swizzle is preserved
+                        v.x = corr_word(v.x); v.y = corr_word(v.y); v.z = corr_word(v.z); v.w = corr_word(v.w);
+                        dst[j * 128 + t] = v;
+                    }
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // make the writes visible to the tensor core
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(corr_bar(s));
                 }
-                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // make the writes visible to the tensor core
-                __syncwarp();
-                if (lane == 0) mbar_arrive(corr_bar(s));
             }
         }
-        if (ok) ok = mbar_wait(accum_bar, 0, abort_flag);
-        ok = __all_sync(0xFFFFFFFFu, ok && !*abort_flag);
-        if (ok) {
+    } else {
+        // ------------------------------------------------------------------ epilogue
+        const int q = warp & 3;                               // TMEM lane quarter this warp may read
+        uint32_t* tile = reinterpret_cast<uint32_t*>(epi_ptr + (warp - 6) * 4096);
+        const bool split = p.ksplit > 1;
+        int i = 0;
+        bool ok = true;
+        for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x, ++i) {
+            const Unit w = get_unit(p, u);
+            const int buf = i & 1;
+            ok = mbar_wait(acc_full_bar(buf), (i >> 1) & 1, abort_flag);
+            ok = __all_sync(0xFFFFFFFFu, ok && !*abort_flag);
+            if (!ok) break;
             tc_fence_after();
-            const int q = warp & 3;                               // TMEM lane quarter this warp may read
-            const int n = n_tile * kTileW + q * 32 + lane;
-            const float bias = (p.bias != nullptr && n < p.N) ? __bfloat162float(p.bias[n]) : 0.0f;
-            const bool has_bias = p.bias != nullptr;
+            const int n0 = w.n_tile * kTileW + q * 32;        // first output column of this warp
+            const int n = n0 + lane;
+            const float bias = (!split && p.bias != nullptr && n < p.N) ? __bfloat162float(p.bias[n]) : 0.0f;
+            const bool has_bias = !split && p.bias != nullptr;
 #pragma unroll 1
             for (int c0 = 0; c0 < BN; c0 += 32) {
-                const int m0 = m_tile * BN + c0;
+                const int m0 = w.m_tile * BN + c0;
                 if (m0 >= p.M) break;                             // uniform across the warp
                 uint32_t v[32];
-                tc_ld_32x32(tmem + ((uint32_t)(q * 32) << 16) + c0, v);
-                if (n < p.N) {
+                tc_ld_32x32(tmem + buf * C::kAccStride + ((uint32_t)(q * 32) << 16) + c0, v);
+                if (c0 + 32 >= BN || m0 + 32 >= p.M) {            // last read of this accumulator: hand it back
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(acc_empty_bar(buf));
+                }
+                if (split) {
+                    // float32 partial sums, [ksp][m][n]
+                    float* dstp = p.partial + ((int64_t)w.ksp * p.M) * p.N;
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) {
-                        if (m0 + j < p.M) {
-                            __nv_bfloat16 y = __float2bfloat16_rn(__uint_as_float(v[j]));
-                            if (has_bias) y = __float2bfloat16_rn(__bfloat162float(y) + bias);   // `output += bias` in bf16
-                            p.out[(int64_t)(m0 + j) * p.ldo + n] = y;
+                    for (int j = 0; j < 32; ++j) tile[j * 32 + lane] = v[j];
+                    __syncwarp();
+                    const bool vec = (p.N % 4 == 0) && (n0 + 32 <= p.N);
+#pragma unroll
+                    for (int r = 0; r < 4; ++r) {
+                        const int row = r * 8 + (lane >> 2), seg = lane & 3;
+                        const int m = m0 + row;
+                        if (m < p.M) {
+                            if (vec) {
+#pragma unroll
+                                for (int h = 0; h < 2; ++h)
+                                    *reinterpret_cast<uint4*>(dstp + (int64_t)m * p.N + n0 + seg * 8 + h * 4) =
+                                        *reinterpret_cast<const uint4*>(tile + row * 32 + seg * 8 + h * 4);
+                            } else {
+                                for (int e = 0; e < 8; ++e)
+                                    if (n0 + seg * 8 + e < p.N) dstp[(int64_t)m * p.N + n0 + seg * 8 + e] = __uint_as_float(tile[row * 32 + seg * 8 + e]);
+                            }
                         }
                     }
+                    __syncwarp();
+                } else {
+                    // bf16 output: transpose a 32(m) x 32(n) block through shared memory so that each row of 32
+                    // consecutive n (64 bytes) is written with 16-byte stores
+                    __nv_bfloat16* t16 = reinterpret_cast<__nv_bfloat16*>(tile);
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        __nv_bfloat16 y = __float2bfloat16_rn(__uint_as_float(v[j]));
+                        if (has_bias) y = __float2bfloat16_rn(__bfloat162float(y) + bias);   // `output += bias` in bf16
+                        t16[j * 32 + lane] = y;
+                    }
+                    __syncwarp();
+                    const bool vec = (p.ldo % 8 == 0) && (((uintptr_t)p.out) % 16 == 0) && (n0 + 32 <= p.N);
+#pragma unroll
+                    for (int r = 0; r < 4; ++r) {
+                        const int row = r * 8 + (lane >> 2), seg = lane & 3;
+                        const int m = m0 + row;
+                        if (m < p.M) {
+                            if (vec) {
+                                *reinterpret_cast<uint4*>(p.out + (int64_t)m * p.ldo + n0 + seg * 8) =
+                                    *reinterpret_cast<const uint4*>(t16 + row * 32 + seg * 8);
+                            } else {
+                                for (int e = 0; e < 8; ++e)
+                                    if (n0 + seg * 8 + e < p.N) p.out[(int64_t)m * p.ldo + n0 + seg * 8 + e] = t16[row * 32 + seg * 8 + e];
+                            }
+                        }
+                    }
+                    __syncwarp();
                 }
             }
         }
@@ -329,6 +441,21 @@ __global__ void __launch_bounds__(192, 1) gemm_mxf4_kernel(const __grid_constant
     if (warp == 1) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(C::kTmemCols) : "memory");
+    }
+}
+
+// Sums the K-split partials, rounds to bf16, adds the bias: out[m][n] = bf16(bf16(sum_s partial[s][m][n]) + bias[n]).
+// The order of the sum is fixed, so the result does not depend on scheduling.
+__global__ void __launch_bounds__(256) splitk_reduce_kernel(const float* __restrict__ partial, int ksplit, int64_t M, int64_t N,
+                                                            const __nv_bfloat16* __restrict__ bias, __nv_bfloat16* __restrict__ out, int64_t ldo) {
+    const int64_t total = M * N;
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        float acc = 0.0f;
+        for (int s = 0; s < ksplit; ++s) acc += partial[(int64_t)s * total + i];
+        const int64_t m = i / N, n = i - m * N;
+        __nv_bfloat16 y = __float2bfloat16_rn(acc);
+        if (bias) y = __float2bfloat16_rn(__bfloat162float(y) + __bfloat162float(bias[n]));
+        out[m * ldo + n] = y;
     }
 }
 
@@ -363,7 +490,7 @@ int make_map(CUtensorMap* map, const void* ptr, int64_t rows, int64_t row_bytes,
 }
 
 template <int BN>
-int launch_gemm(const CUtensorMap& mw, const CUtensorMap& mx, const GemmParams& p, cudaStream_t st) {
+int launch_gemm(const CUtensorMap& mw, const CUtensorMap& mx, GemmParams& p, cudaStream_t st) {
     using C = Cfg<BN>;
     static bool configured[64] = {false};
     int dev = 0;
@@ -373,27 +500,64 @@ int launch_gemm(const CUtensorMap& mw, const CUtensorMap& mx, const GemmParams& 
         if (e != cudaSuccess) return cuda_fail(e, "mxfp4_gemm: cudaFuncSetAttribute");
         configured[dev] = true;
     }
-    dim3 grid((p.N + kTileW - 1) / kTileW, (p.M + BN - 1) / BN);
-    gemm_mxf4_kernel<BN><<<grid, 192, C::kSmemBytes, st>>>(mw, mx, p);
+    p.m_tiles = (p.M + BN - 1) / BN;
+    const int64_t units = (int64_t)p.n_tiles * p.m_tiles * p.ksplit;
+    const int grid = (int)(units < num_sms() ? units : num_sms());      // persistent: at most one CTA per SM
+    gemm_mxf4_kernel<BN><<<grid, kThreads, C::kSmemBytes, st>>>(mw, mx, p);
     MXFP4_CHECK_LAUNCH("mxfp4_gemm (tcgen05 kernel)");
     return MXFP4_OK;
 }
 
 inline int64_t align_up(int64_t v, int64_t a) { return (v + a - 1) / a * a; }
 
+// Activation-tile width (the MMA's N): the narrowest tile that covers a small M; for large M, 192 unless its
+// padding wastes more than 4 %.
+int pick_bn(int64_t M) {
+    if (M <= 32) return 32;
+    if (M <= 64) return 64;
+    if (M <= 128) return 128;
+    const int64_t pad192 = (M + 191) / 192 * 192;
+    return pad192 * 100 <= M * 104 ? 192 : 128;
+}
+
+// Number of K ranges.  Skinny problems have fewer tiles than SMs; cutting K spreads the weight stream over
+// the whole chip.  Cost model in units of one pipeline stage: rounds * (stages per unit + fixed cost per unit)
+// + a fixed cost for the reduction.
+int pick_ksplit(int64_t M, int64_t N, int64_t K) {
+    const int64_t nks = (K + kStageK - 1) / kStageK;
+    if (M > 128 || nks < 2) return 1;
+    const int64_t tiles = (N + kTileW - 1) / kTileW;     // M <= 128: one activation tile
+    const int64_t sms = num_sms();
+    int best = 1;
+    int64_t best_cost = (tiles + sms - 1) / sms * (nks + 2);
+    for (int ks = 2; ks <= 32 && ks <= nks; ++ks) {
+        const int64_t rounds = (tiles * ks + sms - 1) / sms;
+        const int64_t cost = rounds * ((nks + ks - 1) / ks + 2) + 3;
+        if (cost < best_cost) { best_cost = cost; best = ks; }
+    }
+    return best;
+}
+
 }  // namespace
 }  // namespace mxfp4
 
+extern "C" int64_t mxfp4_gemm_splitk_bytes(int64_t M, int64_t N, int64_t K) {
+    if (M <= 0 || N <= 0 || K <= 0) return 0;
+    const int ks = mxfp4::pick_ksplit(M, N, K);
+    return ks > 1 ? (int64_t)ks * M * N * 4 : 0;
+}
+
 extern "C" int64_t mxfp4_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K, int mode) {
-    (void)N; (void)mode;
+    (void)mode;
     if (M <= 0 || K <= 0) return 0;
-    // [status word, 256 B] [packed activations M*K/2] [blocked activation scales]
-    return 256 + mxfp4::align_up(M * (K / 2), 256) + mxfp4_act_scales_bytes(M, K);
+    // [status word, 256 B] [packed activations M*K/2] [blocked activation scales] [K-split partial sums]
+    return 256 + mxfp4::align_up(M * (K / 2), 256) + mxfp4::align_up(mxfp4_act_scales_bytes(M, K), 256) + mxfp4_gemm_splitk_bytes(M, N, K);
 }
 
 extern "C" int mxfp4_gemm_prequantized(const uint8_t* a_packed, const uint8_t* a_sf_blocked, const uint8_t* w_packed,
                                        const uint8_t* w_sf_prepared, const void* bias_bf16, void* out_bf16, int64_t ldo, int64_t M,
-                                       int64_t N, int64_t K, int mode, int* status_dev, void* stream) {
+                                       int64_t N, int64_t K, int mode, void* splitk_workspace, int64_t splitk_bytes, int* status_dev,
+                                       void* stream) {
     using namespace mxfp4;
     if (M < 0 || N < 0 || K < 0) { set_error("mxfp4_gemm: negative size"); return MXFP4_E_SHAPE; }
     if (M == 0 || N == 0) return MXFP4_OK;
@@ -407,22 +571,40 @@ extern "C" int mxfp4_gemm_prequantized(const uint8_t* a_packed, const uint8_t* a
         return MXFP4_E_ALIGN;
     }
     CUtensorMap mw, mx;
-    const int bn = M <= 32 ? 32 : (M <= 64 ? 64 : (M <= 128 ? 128 : 256));
+    const int bn = pick_bn(M);
     int rc = make_map(&mw, w_packed, N, K / 2, kTileW);
     if (rc) return rc;
     rc = make_map(&mx, a_packed, M, K / 2, bn);
     if (rc) return rc;
     GemmParams p;
     p.sfw = w_sf_prepared; p.sfx = a_sf_blocked; p.bias = (const __nv_bfloat16*)bias_bf16; p.out = (__nv_bfloat16*)out_bf16;
+    p.partial = nullptr;
     p.ldo = ldo; p.M = (int)M; p.N = (int)N; p.K = (int)K; p.kstages = (int)((K + kStageK - 1) / kStageK);
+    p.n_tiles = (int)((N + kTileW - 1) / kTileW); p.m_tiles = 0;
+    p.ksplit = 1;
+    const int want = pick_ksplit(M, N, K);
+    if (want > 1 && splitk_workspace != nullptr && splitk_bytes >= (int64_t)want * M * N * 4 && (uintptr_t)splitk_workspace % 16 == 0) {
+        p.ksplit = want;
+        p.partial = (float*)splitk_workspace;
+    }
     p.exact = mode == MXFP4_GEMM_EXACT; p.status = status_dev;
     cudaStream_t st = (cudaStream_t)stream;
     switch (bn) {
-        case 32: return launch_gemm<32>(mw, mx, p, st);
-        case 64: return launch_gemm<64>(mw, mx, p, st);
-        case 128: return launch_gemm<128>(mw, mx, p, st);
-        default: return launch_gemm<256>(mw, mx, p, st);
+        case 32: rc = launch_gemm<32>(mw, mx, p, st); break;
+        case 64: rc = launch_gemm<64>(mw, mx, p, st); break;
+        case 128: rc = launch_gemm<128>(mw, mx, p, st); break;
+        default: rc = launch_gemm<192>(mw, mx, p, st); break;
     }
+    if (rc) return rc;
+    if (p.ksplit > 1) {
+        const int64_t total = M * N;
+        int64_t grid = (total + 255) / 256;
+        const int64_t cap = (int64_t)num_sms() * 16;
+        if (grid > cap) grid = cap;
+        splitk_reduce_kernel<<<(unsigned)grid, 256, 0, st>>>(p.partial, p.ksplit, M, N, p.bias, p.out, ldo);
+        MXFP4_CHECK_LAUNCH("mxfp4_gemm (split-K reduction)");
+    }
+    return MXFP4_OK;
 }
 
 extern "C" int mxfp4_gemm(const void* x_bf16, int64_t ldx, const uint8_t* w_packed, const uint8_t* w_sf_prepared, const void* bias_bf16,
@@ -442,7 +624,9 @@ extern "C" int mxfp4_gemm(const void* x_bf16, int64_t ldx, const uint8_t* w_pack
     int* status = (int*)ws;
     uint8_t* a_packed = ws + 256;
     uint8_t* a_sf = a_packed + align_up(M * (K / 2), 256);
+    uint8_t* partial = a_sf + align_up(mxfp4_act_scales_bytes(M, K), 256);
     int rc = mxfp4_act_quantize(x_bf16, M, K, ldx, a_packed, a_sf, stream);
     if (rc) return rc;
-    return mxfp4_gemm_prequantized(a_packed, a_sf, w_packed, w_sf_prepared, bias_bf16, out_bf16, ldo, M, N, K, mode, status, stream);
+    return mxfp4_gemm_prequantized(a_packed, a_sf, w_packed, w_sf_prepared, bias_bf16, out_bf16, ldo, M, N, K, mode, partial,
+                                   mxfp4_gemm_splitk_bytes(M, N, K), status, stream);
 }

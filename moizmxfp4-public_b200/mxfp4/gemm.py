@@ -7,6 +7,7 @@ activations.
 """
 import os
 import threading
+import weakref
 from collections import OrderedDict
 from typing import Optional
 
@@ -16,8 +17,8 @@ from . import _capi
 
 _MODES = {"exact": _capi.GEMM_EXACT, "fast": _capi.GEMM_FAST}
 _mode = _MODES[os.environ.get("MXFP4_GEMM_MODE", "exact")]
-_lock = threading.Lock()
-_prepared = OrderedDict()        # (ptr, numel, device index, version) -> prepared scale tensor
+_lock = threading.RLock()
+_prepared = OrderedDict()        # id(scale tensor) -> (weakref, version, (N, K, ptr), prepared scale tensor)
 _PREPARED_MAX = 4096
 _workspaces = {}                 # (device index, stream) -> uint8 tensor
 
@@ -34,22 +35,35 @@ def get_gemm_mode() -> str:
 
 
 def prepared_scales(weight_scales: torch.Tensor, N: int, K: int) -> torch.Tensor:
-    """Tensor-core layout of a weight's E8M0 scales, cached by storage identity and version counter
-    (an in-place update such as load_state_dict bumps the version and invalidates the entry)."""
-    key = (weight_scales.data_ptr(), weight_scales.numel(), weight_scales.device.index, weight_scales._version)
+    """Tensor-core layout of a weight's E8M0 scales.
+
+    Cached per live tensor OBJECT (a weak reference guards against a recycled address) and per version
+    counter (an in-place update such as load_state_dict invalidates the entry).  A module's buffer hits
+    the cache on every forward; a temporary tensor simply pays one small re-tiling kernel."""
+    key = id(weight_scales)
     with _lock:
         hit = _prepared.get(key)
         if hit is not None:
-            _prepared.move_to_end(key)
-            return hit
+            ref, version, shape, prepared = hit
+            if ref() is weight_scales and version == weight_scales._version and shape == (N, K, weight_scales.data_ptr()):
+                _prepared.move_to_end(key)
+                return prepared
+            del _prepared[key]
     L = _capi.load()
     ws = weight_scales.contiguous()
     out = torch.empty(L.mxfp4_prepared_scales_bytes(N, K), dtype=torch.uint8, device=ws.device)
     with torch.cuda.device(ws.device):
         _capi.check(L.mxfp4_prepare_weight_scales(ws.data_ptr(), N, K, out.data_ptr(), _capi.stream_ptr(ws.device)),
                     "mxfp4_prepare_weight_scales")
+
+    def _drop(_ref, key=key):
+        with _lock:
+            ent = _prepared.get(key)
+            if ent is not None and ent[0] is _ref:
+                del _prepared[key]
+
     with _lock:
-        _prepared[key] = out
+        _prepared[key] = (weakref.ref(weight_scales, _drop), weight_scales._version, (N, K, weight_scales.data_ptr()), out)
         while len(_prepared) > _PREPARED_MAX:
             _prepared.popitem(last=False)
     return out
