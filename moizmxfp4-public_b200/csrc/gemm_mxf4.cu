@@ -14,8 +14,9 @@
 //
 // Tiling: one CTA computes a 128 (weight rows, the MMA's M / TMEM lanes) x BN (activation rows, the
 // MMA's N / TMEM columns) tile of out^T.  K advances in stages of 256 elements (128 bytes per row,
-// one 128-byte swizzle span), 4 MMAs of K=64 per stage and pass.
-// Warps: 0 = TMA producer, 1 = MMA issuer (owns TMEM), 2..5 = correction transform, then epilogue.
+// one 128-byte swizzle span), 4 MMAs of K=64 per stage and pass.  The grid is persistent (one CTA per SM)
+// and walks a list of work units (K range, weight tile, activation tile).
+// Warps: 0 = TMA producer, 1 = MMA issuer (owns TMEM), 2..5 = correction transform, 6..9 = epilogue.
 // Every wait is bounded; a wait that runs out records MXFP4_E_TIMEOUT in the status word and the
 // CTA drains and exits.
 #include <cuda.h>
@@ -148,13 +149,15 @@ struct Cfg {
     static constexpr int kSmemBytes = kStages * kStageBytes + kEpiBytes + 1024 + 512;
     static constexpr uint32_t kTxBytes = kWBytes + kXBytes + kSfwBytes + kSfxBytes;
     // tensor-memory columns: two accumulators, then scale factors
-    static constexpr int kAccStride = BN <= 128 ? 128 : 192;
-    static constexpr int kColSf = 2 * kAccStride;
+    // two accumulators (epilogue of one unit overlaps the MMAs of the next) when they fit beside the scale factors
+    static constexpr int kAccBufs = BN <= 192 ? 2 : 1;
+    static constexpr int kAccStride = BN <= 128 ? 128 : (BN <= 192 ? 192 : 256);
+    static constexpr int kColSf = kAccBufs * kAccStride;
     static constexpr int kColSfw = kColSf;         // 2 K-tiles x 4 columns (pass 1)
     static constexpr int kColSfw2 = kColSf + 8;    // same for pass 2
     static constexpr int kColSfx = kColSf + 16;    // 2 K-tiles x 4*kXT columns
     static constexpr int kTmemCols = 512;
-    static_assert(BN % 32 == 0 && BN <= 192, "tile width");
+    static_assert(BN % 32 == 0 && BN <= 256, "tile width");
     static_assert(kColSfx + 8 * kXT <= 512, "tensor memory budget");
     static_assert(kStages >= 2, "pipeline depth");
 };
@@ -276,11 +279,12 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_mxf4_kernel(const __grid_con
             bool ok = true;
             for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x, ++i) {
                 const Unit w = get_unit(p, u);
-                const int buf = i & 1;
+                const int buf = i % C::kAccBufs;
+                const uint32_t acc_ph = (i / C::kAccBufs) & 1;
                 const uint32_t acc = tmem + buf * C::kAccStride;
                 // activation scales of a tile that starts inside a 128-row group sit at a column offset
                 const uint32_t sfx_col = tmem + C::kColSfx + ((w.m_tile * BN) % 128) / 32;
-                ok = mbar_wait(acc_empty_bar(buf), ((i >> 1) & 1) ^ 1u, abort_flag);   // epilogue has drained this buffer
+                ok = mbar_wait(acc_empty_bar(buf), acc_ph ^ 1u, abort_flag);   // epilogue has drained this buffer
                 if (!ok) break;
                 tc_fence_after();
                 for (int ks = w.ks0; ks < w.ks1; ++ks, ++it) {
@@ -352,8 +356,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_mxf4_kernel(const __grid_con
         bool ok = true;
         for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x, ++i) {
             const Unit w = get_unit(p, u);
-            const int buf = i & 1;
-            ok = mbar_wait(acc_full_bar(buf), (i >> 1) & 1, abort_flag);
+            const int buf = i % C::kAccBufs;
+            ok = mbar_wait(acc_full_bar(buf), (i / C::kAccBufs) & 1, abort_flag);
             ok = __all_sync(0xFFFFFFFFu, ok && !*abort_flag);
             if (!ok) break;
             tc_fence_after();
@@ -516,7 +520,8 @@ int pick_bn(int64_t M) {
     if (M <= 32) return 32;
     if (M <= 64) return 64;
     if (M <= 128) return 128;
-    const int64_t pad192 = (M + 191) / 192 * 192;
+    const int64_t pad256 = (M + 255) / 256 * 256, pad192 = (M + 191) / 192 * 192;
+    if (pad256 * 100 <= M * 104) return 256;      // widest tile: fewest shared-memory bytes per MAC
     return pad192 * 100 <= M * 104 ? 192 : 128;
 }
 
@@ -593,7 +598,8 @@ extern "C" int mxfp4_gemm_prequantized(const uint8_t* a_packed, const uint8_t* a
         case 32: rc = launch_gemm<32>(mw, mx, p, st); break;
         case 64: rc = launch_gemm<64>(mw, mx, p, st); break;
         case 128: rc = launch_gemm<128>(mw, mx, p, st); break;
-        default: rc = launch_gemm<192>(mw, mx, p, st); break;
+        case 192: rc = launch_gemm<192>(mw, mx, p, st); break;
+        default: rc = launch_gemm<256>(mw, mx, p, st); break;
     }
     if (rc) return rc;
     if (p.ksplit > 1) {

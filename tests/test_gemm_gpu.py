@@ -61,7 +61,7 @@ def test_prepared_weight_scales_layout():
 
 
 SHAPES = [(1, 128, 32), (33, 128, 32), (17, 100, 96), (32, 128, 256), (64, 128, 512), (128, 256, 1024), (129, 256, 1024),
-          (256, 256, 1024), (300, 384, 1376), (1, 4096, 4096), (16, 4096, 4096), (128, 4096, 4096), (1024, 4096, 4096),
+          (256, 256, 1024), (300, 384, 1376), (384, 256, 512), (576, 384, 1024), (1, 4096, 4096), (16, 4096, 4096), (128, 4096, 4096), (1024, 4096, 4096),
           (128, 11008, 4096), (128, 4096, 11008), (2048, 1376, 4096)]
 
 
