@@ -158,7 +158,8 @@ struct Cfg {
     static constexpr int kColSfx = kColSf + 16;    // 2 K-tiles x 4*kXT columns
     static constexpr int kTmemCols = 512;
     static_assert(BN % 32 == 0 && BN <= 256, "tile width");
-    static_assert(kColSfx + 8 * kXT <= 512, "tensor memory budget");
+    static constexpr int kSfSetCols = 32;          // one set of scale-factor columns per pipeline stage
+    static_assert(kColSf + kStages * kSfSetCols <= 512 && 16 + 8 * kXT <= kSfSetCols, "tensor memory budget");
     static_assert(kStages >= 2, "pipeline depth");
 };
 
@@ -177,7 +178,7 @@ struct GemmParams {
     int* status;
 };
 
-constexpr int kThreads = 320;   // warps: 0 producer, 1 MMA, 2-5 transform, 6-9 epilogue
+constexpr int kThreads = 352;   // warps: 0 producer, 1 MMA, 2-5 transform, 6-9 epilogue, 10 scale-factor copier
 
 // A work unit is (k-range, weight tile, activation tile); units are dealt round-robin to the CTAs of
 // a persistent grid.  All roles walk the same unit sequence.
@@ -208,9 +209,10 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_mxf4_kernel(const __grid_con
     auto full_bar = [&](int s) { return bars + 8u * s; };
     auto empty_bar = [&](int s) { return bars + 8u * (C::kStages + s); };
     auto corr_bar = [&](int s) { return bars + 8u * (2 * C::kStages + s); };
-    auto acc_full_bar = [&](int b) { return bars + 8u * (3 * C::kStages + b); };
-    auto acc_empty_bar = [&](int b) { return bars + 8u * (3 * C::kStages + 2 + b); };
-    uint8_t* tail = epi_ptr + C::kEpiBytes + 8 * (3 * C::kStages + 4);
+    auto sf_bar = [&](int s) { return bars + 8u * (3 * C::kStages + s); };
+    auto acc_full_bar = [&](int b) { return bars + 8u * (4 * C::kStages + b); };
+    auto acc_empty_bar = [&](int b) { return bars + 8u * (4 * C::kStages + 2 + b); };
+    uint8_t* tail = epi_ptr + C::kEpiBytes + 8 * (4 * C::kStages + 4);
     volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(tail);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tail + 4);
 
@@ -222,6 +224,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_mxf4_kernel(const __grid_con
             mbar_init(full_bar(s), 1);
             mbar_init(empty_bar(s), 1);
             mbar_init(corr_bar(s), 4);
+            mbar_init(sf_bar(s), 1);
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(acc_full_bar(b), 1);
@@ -283,27 +286,21 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_mxf4_kernel(const __grid_con
                 const uint32_t acc_ph = (i / C::kAccBufs) & 1;
                 const uint32_t acc = tmem + buf * C::kAccStride;
                 // activation scales of a tile that starts inside a 128-row group sit at a column offset
-                const uint32_t sfx_col = tmem + C::kColSfx + ((w.m_tile * BN) % 128) / 32;
+                const uint32_t sfx_off = ((w.m_tile * BN) % 128) / 32;
                 ok = mbar_wait(acc_empty_bar(buf), acc_ph ^ 1u, abort_flag);   // epilogue has drained this buffer
                 if (!ok) break;
                 tc_fence_after();
                 for (int ks = w.ks0; ks < w.ks1; ++ks, ++it) {
                     const int s = it % C::kStages;
                     const uint32_t ph = (it / C::kStages) & 1;
-                    ok = mbar_wait(full_bar(s), ph, abort_flag);
-                    if (ok && p.exact) ok = mbar_wait(corr_bar(s), ph, abort_flag);
+                    ok = mbar_wait(full_bar(s), ph, abort_flag);                   // operand tiles have landed
+                    if (ok) ok = mbar_wait(sf_bar(s), ph, abort_flag);              // scale factors are in tensor memory
+                    if (ok && p.exact) ok = mbar_wait(corr_bar(s), ph, abort_flag); // correction tile is built
                     if (!ok) break;
                     tc_fence_after();
                     const uint32_t st = base + s * C::kStageBytes;
-                    // scale factors: shared memory -> tensor memory (in order with the MMAs on the tensor pipe)
-#pragma unroll
-                    for (int g = 0; g < 2; ++g) {
-                        tc_cp_sf(tmem + C::kColSfw + 4 * g, desc_sf(st + C::kOffSfw + 512 * g));
-                        if (p.exact) tc_cp_sf(tmem + C::kColSfw2 + 4 * g, desc_sf(st + C::kOffSfw + 1024 + 512 * g));
-#pragma unroll
-                        for (int t = 0; t < C::kXT; ++t)
-                            tc_cp_sf(tmem + C::kColSfx + 4 * C::kXT * g + 4 * t, desc_sf(st + C::kOffSfx + 1024 * t + 512 * g));
-                    }
+                    const uint32_t sft = tmem + s * C::kSfSetCols;       // this stage's scale-factor columns
+                    const uint32_t sfx_col = sft + C::kColSfx + sfx_off;
                     const uint64_t wdesc = desc_sw128(st), cdesc = desc_sw128(st + C::kOffC), xdesc = desc_sw128(st + C::kOffX);
 #pragma unroll
                     for (int kb = 0; kb < 4; ++kb) {
@@ -311,8 +308,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_mxf4_kernel(const __grid_con
                         const uint32_t idesc = (kb & 1) ? idesc2 : idesc0;
                         const uint64_t adv = (uint64_t)(kb * 32 >> 4);             // 64 elements = 32 bytes along K
                         const uint32_t sfb = sfx_col + 4 * C::kXT * g;
-                        tc_mma_mxf4(acc, wdesc + adv, xdesc + adv, idesc, tmem + C::kColSfw + 4 * g, sfb, (ks > w.ks0 || kb > 0) ? 1u : 0u);
-                        if (p.exact) tc_mma_mxf4(acc, cdesc + adv, xdesc + adv, idesc, tmem + C::kColSfw2 + 4 * g, sfb, 1u);
+                        tc_mma_mxf4(acc, wdesc + adv, xdesc + adv, idesc, sft + C::kColSfw + 4 * g, sfb, (ks > w.ks0 || kb > 0) ? 1u : 0u);
+                        if (p.exact) tc_mma_mxf4(acc, cdesc + adv, xdesc + adv, idesc, sft + C::kColSfw2 + 4 * g, sfb, 1u);
                     }
                     tc_commit(empty_bar(s));      // frees the stage once these MMAs have read it
                 }
@@ -347,6 +344,38 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_mxf4_kernel(const __grid_con
                 }
             }
         }
+    } else if (warp == 10) {
+        // ------------------------------------------------------------------ scale-factor copier
+        // Shared memory -> tensor memory with tcgen05.cp, one column set per pipeline stage.  Issuing these
+        // copies costs the issuing thread a few hundred cycles per stage, so they live here and not in the MMA
+        // thread; tcgen05.commit tells the MMA thread when a stage's scales are in place.  A set is reused only
+        // after its stage has been refilled, i.e. after the MMAs that read it have completed.
+        if (lane == 0) {
+            uint32_t it = 0;
+            bool ok = true;
+            for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x) {
+                const Unit w = get_unit(p, u);
+                for (int ks = w.ks0; ks < w.ks1; ++ks, ++it) {
+                    const int s = it % C::kStages;
+                    const uint32_t ph = (it / C::kStages) & 1;
+                    ok = mbar_wait(full_bar(s), ph, abort_flag);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint32_t st = base + s * C::kStageBytes;
+                    const uint32_t sft = tmem + s * C::kSfSetCols;
+#pragma unroll
+                    for (int g = 0; g < 2; ++g) {
+                        tc_cp_sf(sft + C::kColSfw + 4 * g, desc_sf(st + C::kOffSfw + 512 * g));
+                        if (p.exact) tc_cp_sf(sft + C::kColSfw2 + 4 * g, desc_sf(st + C::kOffSfw + 1024 + 512 * g));
+#pragma unroll
+                        for (int t = 0; t < C::kXT; ++t)
+                            tc_cp_sf(sft + C::kColSfx + 4 * C::kXT * g + 4 * t, desc_sf(st + C::kOffSfx + 1024 * t + 512 * g));
+                    }
+                    tc_commit(sf_bar(s));
+                }
+            }
+        }
+        __syncwarp();
     } else {
         // ------------------------------------------------------------------ epilogue
         const int q = warp & 3;                               // TMEM lane quarter this warp may read
@@ -365,6 +394,61 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_mxf4_kernel(const __grid_con
             const int n = n0 + lane;
             const float bias = (!split && p.bias != nullptr && n < p.N) ? __bfloat162float(p.bias[n]) : 0.0f;
             const bool has_bias = !split && p.bias != nullptr;
+            if constexpr (C::kAccBufs == 1) {
+                // Single accumulator: drain the whole tile row into registers as bf16 pairs first and hand the
+                // accumulator back at once, so that the next unit's MMAs run while this one is being stored.
+                uint32_t pk[BN / 2];
+#pragma unroll
+                for (int c0 = 0; c0 < BN; c0 += 32) {
+                    if (w.m_tile * BN + c0 < p.M) {               // uniform across the warp
+                        uint32_t v[32];
+                        tc_ld_32x32(tmem + ((uint32_t)(q * 32) << 16) + c0, v);
+#pragma unroll
+                        for (int j = 0; j < 32; j += 2) {
+                            __nv_bfloat16 y0 = __float2bfloat16_rn(__uint_as_float(v[j])), y1 = __float2bfloat16_rn(__uint_as_float(v[j + 1]));
+                            if (has_bias) {                        // `output += bias` in bf16
+                                y0 = __float2bfloat16_rn(__bfloat162float(y0) + bias);
+                                y1 = __float2bfloat16_rn(__bfloat162float(y1) + bias);
+                            }
+                            pk[(c0 + j) / 2] = (uint32_t)__bfloat16_as_ushort(y0) | ((uint32_t)__bfloat16_as_ushort(y1) << 16);
+                        }
+                    }
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(acc_empty_bar(buf));
+                uint16_t* t16 = reinterpret_cast<uint16_t*>(tile);
+                const bool vec = (p.ldo % 8 == 0) && (((uintptr_t)p.out) % 16 == 0) && (n0 + 32 <= p.N);
+#pragma unroll
+                for (int c0 = 0; c0 < BN; c0 += 32) {
+                    const int m0 = w.m_tile * BN + c0;
+                    if (m0 < p.M) {
+#pragma unroll
+                        for (int j = 0; j < 32; j += 2) {
+                            t16[j * 32 + lane] = (uint16_t)(pk[(c0 + j) / 2] & 0xFFFFu);
+                            t16[(j + 1) * 32 + lane] = (uint16_t)(pk[(c0 + j) / 2] >> 16);
+                        }
+                        __syncwarp();
+#pragma unroll
+                        for (int r = 0; r < 4; ++r) {
+                            const int row = r * 8 + (lane >> 2), seg = lane & 3;
+                            const int m = m0 + row;
+                            if (m < p.M) {
+                                if (vec) {
+                                    *reinterpret_cast<uint4*>(p.out + (int64_t)m * p.ldo + n0 + seg * 8) =
+                                        *reinterpret_cast<const uint4*>(t16 + row * 32 + seg * 8);
+                                } else {
+                                    for (int e = 0; e < 8; ++e)
+                                        if (n0 + seg * 8 + e < p.N)
+                                            p.out[(int64_t)m * p.ldo + n0 + seg * 8 + e] = __ushort_as_bfloat16(t16[row * 32 + seg * 8 + e]);
+                                }
+                            }
+                        }
+                        __syncwarp();
+                    }
+                }
+                continue;
+            }
 #pragma unroll 1
             for (int c0 = 0; c0 < BN; c0 += 32) {
                 const int m0 = w.m_tile * BN + c0;
