@@ -235,12 +235,140 @@ def cpu_quantize_baseline(budget_s=12.0):
             "sample": f"{n} x quantize of one 4096x4096 bf16 matrix (C restatement of the reference quantiser, OpenMP)"}
 
 
+# ------------------------------------------------------------------------------------------------
+# gemm workload
+# ------------------------------------------------------------------------------------------------
+def cpu_gemm_baseline(steps=3, rows=GEMM_M // 16):
+    """The reference's own formulation of the path (FallbackBackend.matmul, src/mxfp4/backends.py:295-312:
+    dequantise the whole weight, cast, torch.matmul) through the oracle port, on a slice of the activations."""
+    from oracle import oracle
+    torch.set_num_threads(os.cpu_count())
+    w = weight(GEMM_N, GEMM_K, 1)
+    p, s = oracle.quantize(w)
+    x = torch.randn(rows, GEMM_K, generator=torch.Generator().manual_seed(1000)).to(torch.bfloat16)
+    oracle.matmul_w4a16(x[:8], p, s)
+    t0 = time.time()
+    for _ in range(steps):
+        oracle.matmul_w4a16(x, p, s)
+    dt = (time.time() - t0) / steps
+    return {"value": 2.0 * rows * GEMM_N * GEMM_K / dt / 1e12, "unit": "TFLOP/s", "cores": os.cpu_count(), "kind": "port",
+            "sample": f"{steps} x dequantise-then-matmul of {rows} of the {GEMM_M} activation rows against the full [{GEMM_N},{GEMM_K}] weight "
+                      "(C dequantiser + torch CPU bf16 matmul, all host threads)", "ms_per_step": dt * 1e3}
+
+
+def run_gemm(args, rank, world, local):
+    import mxfp4
+    from mxfp4 import _capi, gemm
+    dev = torch.device("cuda", local)
+    torch.cuda.set_device(dev)
+    L = _capi.load()
+    M, N, K = GEMM_M, GEMM_N, GEMM_K
+    q = mxfp4.MXFP4Quantizer(32, "e8m0")
+    packed, scales = q.quantize(weight(N, K, 1 + rank).to(dev))
+    nbuf = 2                                            # two activation/output sets: 2 x (67 + 180) MB, far beyond L2
+    host_x = [torch.randn(M, K, generator=torch.Generator().manual_seed(1000 + M + i)).to(torch.bfloat16).pin_memory() for i in range(nbuf)]
+    xs = [h.to(dev) for h in host_x]
+    outs = [torch.empty(M, N, dtype=torch.bfloat16, device=dev) for _ in range(nbuf)]
+    flops = 2.0 * M * N * K
+
+    def step(i):
+        gemm.quant_matmul_2d(xs[i % nbuf], packed, scales, None, out=outs[i % nbuf])   # the public quant_matmul path
+
+    for i in range(args.warmup):
+        step(i)
+    gemm.check_status()
+    barrier(world)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local) as cs:
+        e0.record()
+        for i in range(args.steps):
+            step(i)
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1)
+        t_end = time.time() + max(0.0, 0.6 - ms * 1e-3)   # keep the same load up long enough for clock samples
+        i = 0
+        while time.time() < t_end:
+            step(i); i += 1
+        torch.cuda.synchronize()
+    ms = max_over_ranks(ms, world, dev)
+    barrier(world)
+    ms_per_step = ms / args.steps
+    value = world * flops / (ms_per_step * 1e-3) / 1e12
+
+    # dominant kernel alone: the tcgen05 GEMM on pre-quantised activations, events on the launching stream
+    aq = [gemm.act_quantize(x) for x in xs]
+    prep = gemm.prepared_scales(scales, N, K)
+    st = torch.zeros(64, dtype=torch.int32, device=dev)
+    sp = torch.cuda.current_stream(dev).cuda_stream
+    mode = _capi.GEMM_EXACT if gemm.get_gemm_mode() == "exact" else _capi.GEMM_FAST
+    reps = max(args.steps, 10)
+
+    def kern(i):
+        j = i % nbuf
+        rc = L.mxfp4_gemm_prequantized(aq[j][0].data_ptr(), aq[j][1].data_ptr(), packed.data_ptr(), prep.data_ptr(), None, outs[j].data_ptr(),
+                                       N, M, N, K, mode, None, 0, st.data_ptr(), sp)
+        assert rc == 0, _capi.last_error()
+    for i in range(3):
+        kern(i)
+    torch.cuda.synchronize()
+    e0.record()
+    for i in range(reps):
+        kern(i)
+    e1.record()
+    torch.cuda.synchronize()
+    k_ms = e0.elapsed_time(e1) / reps
+    assert int(st[0].item()) == 0, "GEMM kernel reported a timed-out wait"
+    pk = peaks()
+    fp4_peak = 4.0 * pk["bf16_tflops"]
+    roof = {"bound": "tensor", "kernel": f"gemm_mxf4_kernel<256> [{M}x{N}x{K}], {gemm.get_gemm_mode()} mode",
+            "achieved": flops / (k_ms * 1e-3) / 1e12, "peak": fp4_peak, "unit": "TFLOP/s",
+            "peak_source": f"4 x {pk['source']} bf16 cuBLAS burst ({pk['bf16_tflops']} TFLOP/s): MEASURED_PEAKS.json has no FP4 entry",
+            "traffic": GEMM_TRAFFIC_BYTES, "kernel_ms": k_ms, "launches_timed": reps}
+    roof["frac"] = roof["achieved"] / roof["peak"]
+
+    # end to end through the public API with host buffers: H2D of the activations, quant_matmul, D2H of the result
+    host_out = torch.empty(M, N, dtype=torch.bfloat16).pin_memory()
+    stage_x = torch.empty(M, K, dtype=torch.bfloat16, device=dev)
+
+    def e2e_step(i):
+        stage_x.copy_(host_x[i % nbuf], non_blocking=True)
+        y = mxfp4.quant_matmul(stage_x, packed, scales)
+        host_out.copy_(y, non_blocking=True)
+    for i in range(2):
+        e2e_step(i)
+    barrier(world)
+    e0.record()
+    for i in range(args.steps):
+        e2e_step(i)
+    e1.record()
+    torch.cuda.synchronize()
+    e2e_ms = max_over_ranks(e0.elapsed_time(e1), world, dev) / args.steps
+    barrier(world)
+    res = {"metric": "mxfp4_gemm_tflops", "value": value, "unit": "TFLOP/s", "per_gpu_tflops": value / world,
+           "ms_per_step": ms_per_step,
+           "config": {"workload": f"quant_matmul: bf16 activations [{M},{K}] x MXFP4 weight [{N},{K}] (Llama-2-7B gate/up shape of the GEMM sweep), "
+                                  f"bf16 out, fp32 accumulate, {gemm.get_gemm_mode()} mode; step = activation quantiser + GEMM",
+                      "M": M, "N": N, "K": K, "l2": "two activation/output sets of 247 MB rotate; each step touches more than L2"},
+           "dtype": "fp4 (e2m1) x fp4 with e8m0 block scales, fp32 accumulate", "roofline": roof, "gpu_launches": 2 * args.steps,
+           "e2e": {"value": world * flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": M * K * 2, "d2h_bytes_per_step": M * N * 2,
+                   "ms_per_step": e2e_ms},
+           "clocks": cs.summary()}
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        res["cpu_baseline"] = cpu_gemm_baseline()
+    return res
+
+
+# DRAM traffic of one GEMM launch (dram__bytes_read.sum + dram__bytes_write.sum, one ncu capture; see profiles/)
+GEMM_TRAFFIC_BYTES = None
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--workload", default=os.environ.get("MXFP4_BENCH_WORKLOAD", "quantize"), choices=["quantize", "gemm"])
+    ap.add_argument("--workload", default=os.environ.get("MXFP4_BENCH_WORKLOAD", "gemm"), choices=["quantize", "gemm"])
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
@@ -250,18 +378,23 @@ def main():
         rank = int(os.environ.get("RANK", "0"))
         if rank != 0:
             return
-        base = cpu_quantize_baseline(budget_s=max(5.0, 2.0 * args.steps))
-        out = {"impl": "reference", "metric": "mxfp4_quantize_hbm_gbs", "value": base["value"], "unit": "GB/s", "n_gpus": args.gpus,
+        if args.workload == "gemm":
+            base = cpu_gemm_baseline(steps=max(1, min(args.steps, 5)))
+            metric, unit, cfg = "mxfp4_gemm_tflops", "TFLOP/s", f"quant_matmul [{GEMM_M},{GEMM_K}] x [{GEMM_N},{GEMM_K}]; each step a bounded sample: " + base["sample"]
+        else:
+            base = cpu_quantize_baseline(budget_s=max(5.0, 2.0 * args.steps))
+            metric, unit, cfg = "mxfp4_quantize_hbm_gbs", "GB/s", "quantize (bounded sample: one 4096x4096 matrix per step)"
+        out = {"impl": "reference", "metric": metric, "value": base["value"], "unit": unit, "n_gpus": args.gpus,
                "steps": args.steps, "warmup": args.warmup, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-               "dtype": "f32 arithmetic on bf16 input", "data": "synthetic", "config": {"workload": "quantize (bounded sample: one 4096x4096 matrix per step)"},
-               "cpu_baseline": base, "e2e": {"value": base["value"], "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+               "dtype": "bf16 x bf16 (dequantised weight), CPU", "data": "synthetic", "config": {"workload": cfg},
+               "cpu_baseline": base, "e2e": {"value": base["value"], "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
         print(json.dumps(out))
         return
 
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device (the product has no CPU path); use --impl reference for the CPU baseline")
     rank, world, local = dist_setup(args.gpus)
-    res = run_quantize(args, rank, world, local)
+    res = (run_gemm if args.workload == "gemm" else run_quantize)(args, rank, world, local)
     res.update({"n_gpus": world, "steps": args.steps, "warmup": args.warmup, "higher_is_better": True, "scaling": "weak",
                 "vs_baseline": None, "data": "synthetic"})
     if rank == 0:

@@ -332,12 +332,16 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_mxf4_kernel(const __grid_con
                     if (!ok) break;
                     const uint4* src = reinterpret_cast<const uint4*>(base_ptr + s * C::kStageBytes);
                     uint4* dst = reinterpret_cast<uint4*>(base_ptr + s * C::kStageBytes + C::kOffC);
+                    // all loads first, then the bit work, then all stores: eight independent chains per thread
+                    uint4 v[C::kWBytes / 16 / 128];
+#pragma unroll
+                    for (int j = 0; j < C::kWBytes / 16 / 128; ++j) v[j] = src[j * 128 + t];
 #pragma unroll
                     for (int j = 0; j < C::kWBytes / 16 / 128; ++j) {
-                        uint4 v = src[j * 128 + t];           // same offset in and out: the swizzle is preserved
-                        v.x = corr_word(v.x); v.y = corr_word(v.y); v.z = corr_word(v.z); v.w = corr_word(v.w);
-                        dst[j * 128 + t] = v;
+                        v[j].x = corr_word(v[j].x); v[j].y = corr_word(v[j].y); v[j].z = corr_word(v[j].z); v[j].w = corr_word(v[j].w);
                     }
+#pragma unroll
+                    for (int j = 0; j < C::kWBytes / 16 / 128; ++j) dst[j * 128 + t] = v[j];   // same offset in and out: the swizzle is preserved
                     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // make the writes visible to the tensor core
                     __syncwarp();
                     if (lane == 0) mbar_arrive(corr_bar(s));
