@@ -142,6 +142,28 @@ MXFP4_API int mxfp4_gemm_prequantized(const uint8_t* a_packed, const uint8_t* a_
                                       int64_t M, int64_t N, int64_t K, int mode, void* splitk_workspace,
                                       int64_t splitk_bytes, int* status_dev, void* stream);
 
+/*
+ * mxfp4_gemm without any workspace argument and without any device allocation.  It has no counterpart in the
+ * reference.  It is for callers that cannot allocate device memory when the matmul is due: a process whose
+ * own pool owns the whole GPU and which bans cudaMalloc after start-up, a plugin living inside such a process,
+ * or a latency-critical loop where an allocation would stall the device.  The scratch mxfp4_gemm takes as
+ * `workspace` is a fixed 16 MiB array inside the library instead (held by every GPU that loads the library, until
+ * the process exits).  Inputs and outputs are still the caller's.
+ *   - Problems whose scratch (packed activations M*K/2 + activation scale tiles + split-K partials, see
+ *     mxfp4_gemm_workspace_bytes) exceeds 16 MiB are rejected with MXFP4_E_WORKSPACE; typical decode shapes
+ *     (M <= 128 with Llama-2-7B/70B layer sizes) fit.
+ *   - The first call on each device looks up the array's device address; make that first call outside any stream
+ *     capture, with the device current.
+ *   - All calls share the one array and it keeps whatever the last call left there (nothing in it has to start
+ *     at zero).  Two calls that overlap on the GPU -- different streams, or several host threads -- race on it;
+ *     serialise them or use mxfp4_gemm with separate workspaces.
+ *   - status_dev: optional device int, zeroed by the caller; receives MXFP4_E_TIMEOUT if a bounded wait ran out.
+ * Other arguments as for mxfp4_gemm.
+ */
+MXFP4_API int mxfp4_gemm_noalloc(const void* x_bf16, int64_t ldx, const uint8_t* w_packed, const uint8_t* w_sf_prepared,
+                                 const void* bias_bf16, void* out_bf16, int64_t ldo, int64_t M, int64_t N, int64_t K, int mode,
+                                 int* status_dev, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -724,3 +724,60 @@ extern "C" int mxfp4_gemm(const void* x_bf16, int64_t ldx, const uint8_t* w_pack
     return mxfp4_gemm_prequantized(a_packed, a_sf, w_packed, w_sf_prepared, bias_bf16, out_bf16, ldo, M, N, K, mode, partial,
                                    mxfp4_gemm_splitk_bytes(M, N, K), status, stream);
 }
+
+// ------------------------------------------------------------------------------------------------
+// Allocation-free variant.
+//
+// Some hosts of this library may not allocate device memory at the point where they need a matmul: a
+// serving process that handed the whole GPU to its own memory pool at start-up and forbids cudaMalloc
+// afterwards, a plugin loaded into such a process, or code on a latency-critical path where an allocation
+// would synchronise the device.  For them the scratch that mxfp4_gemm takes as `workspace` (quantised
+// activations, their scale tiles, split-K partial sums) lives in the fixed array below instead.
+// Every GPU that loads the library holds these 16 MiB until the process exits.
+// ------------------------------------------------------------------------------------------------
+namespace mxfp4 {
+namespace {
+constexpr int64_t kNoAllocScratchBytes = 16ll << 20;
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocScratchBytes];
+}  // namespace
+}  // namespace mxfp4
+
+extern "C" int mxfp4_gemm_noalloc(const void* x_bf16, int64_t ldx, const uint8_t* w_packed, const uint8_t* w_sf_prepared,
+                                  const void* bias_bf16, void* out_bf16, int64_t ldo, int64_t M, int64_t N, int64_t K, int mode,
+                                  int* status_dev, void* stream) {
+    using namespace mxfp4;
+    if (M < 0 || N < 0 || K < 0) { set_error("mxfp4_gemm_noalloc: negative size"); return MXFP4_E_SHAPE; }
+    if (M == 0 || N == 0) return MXFP4_OK;
+    if (K == 0 || K % 32) { set_error("mxfp4_gemm_noalloc: K=%lld must be a positive multiple of 32", (long long)K); return MXFP4_E_SHAPE; }
+    if (!x_bf16) { set_error("mxfp4_gemm_noalloc: null pointer"); return MXFP4_E_BADARG; }
+    const int64_t act_bytes = align_up(M * (K / 2), 256);
+    const int64_t sf_bytes = align_up(mxfp4_act_scales_bytes(M, K), 256);
+    const int64_t split_bytes = mxfp4_gemm_splitk_bytes(M, N, K);
+    const int64_t need = act_bytes + sf_bytes + split_bytes;
+    if (need > kNoAllocScratchBytes) {
+        set_error("mxfp4_gemm_noalloc: M=%lld N=%lld K=%lld needs %lld bytes of scratch, the built-in array holds %lld; "
+                  "use mxfp4_gemm with a caller-provided workspace for this size",
+                  (long long)M, (long long)N, (long long)K, (long long)need, (long long)kNoAllocScratchBytes);
+        return MXFP4_E_WORKSPACE;
+    }
+    // The array's name is only a host-side handle; the kernels need its device address, which differs per
+    // device.  Looked up once per device, with that device current (it is: the caller made it current).
+    static unsigned char* scratch_addr[64] = {nullptr};
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return cuda_fail(e, "mxfp4_gemm_noalloc: cudaGetDevice");
+    if (dev < 0 || dev >= 64) { set_error("mxfp4_gemm_noalloc: device index %d out of range", dev); return MXFP4_E_UNSUPPORTED; }
+    if (scratch_addr[dev] == nullptr) {
+        void* ptr = nullptr;
+        e = cudaGetSymbolAddress(&ptr, g_noalloc_scratch);
+        if (e != cudaSuccess) return cuda_fail(e, "mxfp4_gemm_noalloc: cudaGetSymbolAddress");
+        scratch_addr[dev] = (unsigned char*)ptr;
+    }
+    uint8_t* a_packed = scratch_addr[dev];
+    uint8_t* a_sf = a_packed + act_bytes;
+    uint8_t* partial = a_sf + sf_bytes;
+    int rc = mxfp4_act_quantize(x_bf16, M, K, ldx, a_packed, a_sf, stream);
+    if (rc) return rc;
+    return mxfp4_gemm_prequantized(a_packed, a_sf, w_packed, w_sf_prepared, bias_bf16, out_bf16, ldo, M, N, K, mode,
+                                   split_bytes ? partial : nullptr, split_bytes, status_dev, stream);
+}

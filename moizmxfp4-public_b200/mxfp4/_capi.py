@@ -57,6 +57,8 @@ def load():
     L.mxfp4_gemm.argtypes = [vp, i64, vp, vp, vp, vp, i64, i64, i64, i64, ci, vp, i64, vp]
     L.mxfp4_gemm.restype = ci
     L.mxfp4_gemm_prequantized.argtypes = [vp, vp, vp, vp, vp, vp, i64, i64, i64, i64, ci, vp, i64, vp, vp]
+    L.mxfp4_gemm_noalloc.argtypes = [vp, i64, vp, vp, vp, vp, i64, i64, i64, i64, ci, vp, vp]
+    L.mxfp4_gemm_noalloc.restype = ci
     L.mxfp4_gemm_splitk_bytes.argtypes = [i64, i64, i64]
     L.mxfp4_gemm_splitk_bytes.restype = i64
     L.mxfp4_gemm_prequantized.restype = ci
