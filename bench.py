@@ -359,6 +359,94 @@ def run_gemm(args, rank, world, local):
     return res
 
 
+# ------------------------------------------------------------------------------------------------
+# stack workload: 32-layer Llama-2-7B-shaped MXLinear block stack, tensor-parallel over the ranks
+# ------------------------------------------------------------------------------------------------
+def run_stack(args, rank, world, local):
+    from mxfp4 import gemm
+    from mxfp4.parallel import MXBlockStack
+    dev = torch.device("cuda", local)
+    torch.cuda.set_device(dev)
+    stack = MXBlockStack.build(n_layers=32, device=dev)           # sharded over the default process group when world > 1
+    out = {}
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    cs_sum = None
+    for name, M, steps in (("decode_M128", 128, args.steps), ("prefill_M2048", 2048, max(2, args.steps // 4))):
+        x = torch.randn(M, 4096, generator=torch.Generator().manual_seed(M)).to(torch.bfloat16).to(dev)
+        with torch.no_grad():
+            for _ in range(args.warmup):
+                stack(x)
+            gemm.check_status()
+            barrier(world)
+            with ClockSampler(local) as cs:
+                e0.record()
+                for _ in range(steps):
+                    y = stack(x)
+                e1.record()
+                torch.cuda.synchronize()
+            ms = max_over_ranks(e0.elapsed_time(e1), world, dev) / steps
+            barrier(world)
+        out[name] = {"ms_per_step": ms, "tokens_per_s": M / (ms * 1e-3), "finite": bool(torch.isfinite(y.float()).all().item())}
+        cs_sum = cs.summary()
+    w_elems = 32 * (4 * 4096 * 4096 + 3 * 11008 * 4096)
+    dec = out["decode_M128"]
+    res = {"metric": "mxlinear_stack_decode_tokens_per_s", "value": dec["tokens_per_s"], "unit": "tokens/s", "ms_per_step": dec["ms_per_step"],
+           "config": {"workload": "32 x (q,k,v,o 4096x4096; gate,up 11008x4096; down 4096x11008) MXLinear block stack, 128-token decode step; "
+                                  "also a 2048-token prefill; column/row tensor-parallel over the ranks (2 NCCL all-reduces per layer)",
+                      "parallelism": f"tp{world}", "l2": "3.44 GB of packed weights per step, larger than L2"},
+           "dtype": "fp4 x fp4, e8m0 block scales, fp32 accumulate", "stack": out, "gpu_launches": 32 * 7 * 2 * args.steps,
+           "roofline": {"bound": "hbm", "kernel": "whole decode step (weights streamed once)", "achieved": w_elems * (0.5 + 1 / 32) / world / (dec["ms_per_step"] * 1e-3) / 1e9,
+                        "peak": peaks()["hbm_gbs"], "unit": "GB/s", "traffic": None},
+           "clocks": cs_sum, "scaling_note": "strong"}
+    res["roofline"]["frac"] = res["roofline"]["achieved"] / res["roofline"]["peak"]
+    return res
+
+
+# ------------------------------------------------------------------------------------------------
+# decode workload: random-init Llama-2-7B architecture, quantize_model_mxfp4, greedy decode (one GPU)
+# ------------------------------------------------------------------------------------------------
+def run_decode(args, rank, world, local):
+    import mxfp4
+    from mxfp4 import gemm
+    from transformers import LlamaConfig, LlamaForCausalLM
+    dev = torch.device("cuda", local)
+    torch.cuda.set_device(dev)
+    cfg = LlamaConfig(hidden_size=4096, intermediate_size=11008, num_hidden_layers=32, num_attention_heads=32, num_key_value_heads=32,
+                      vocab_size=32000, max_position_embeddings=4096, torch_dtype=torch.bfloat16)
+    torch.manual_seed(0)
+    with torch.device(dev):
+        model = LlamaForCausalLM(cfg).to(torch.bfloat16).eval()
+    n_lin = sum(m.weight.numel() for m in model.modules() if isinstance(m, torch.nn.Linear))
+    torch.cuda.synchronize()
+    t0 = time.time()
+    mxfp4.quantize_model_mxfp4(model, verbose=False)
+    torch.cuda.synchronize()
+    t_quant = time.time() - t0
+    batch, prompt, new = 128, 512, 128
+    ids = torch.randint(0, 32000, (batch, prompt), generator=torch.Generator().manual_seed(4)).to(dev)
+    with torch.no_grad():
+        model.generate(ids[:2, :16], max_new_tokens=4, do_sample=False)        # warm-up of kernels and caches
+        torch.cuda.synchronize()
+        with ClockSampler(local) as cs:
+            t0 = time.time()
+            model(ids[:, :prompt])                                              # prefill alone, to separate it from decode
+            torch.cuda.synchronize()
+            t_prefill = time.time() - t0
+            t0 = time.time()
+            out = model.generate(ids, max_new_tokens=new, min_new_tokens=new, do_sample=False)
+            torch.cuda.synchronize()
+            t_gen = time.time() - t0
+    gemm.check_status()
+    t_dec = max(t_gen - t_prefill, 1e-9)
+    return {"metric": "llama7b_shape_decode_tokens_per_s", "value": batch * new / t_dec, "unit": "tokens/s", "ms_per_step": t_dec / new * 1e3,
+            "config": {"workload": "random-init Llama-2-7B architecture (HF LlamaForCausalLM), quantize_model_mxfp4 (225 Linear incl. lm_head), "
+                                   "greedy decode of 128 new tokens at batch 128 from 512-token random prompts; HF generate loop and attention",
+                       "parallelism": "tp1"},
+            "dtype": "fp4 x fp4 linear layers, bf16 elsewhere", "generate_s": t_gen, "prefill_s": t_prefill, "new_tokens": int(out.shape[1] - prompt),
+            "quantize_model": {"seconds": t_quant, "linear_elements": n_lin, "gbs": n_lin * QUANT_BYTES_PER_ELEM / t_quant / 1e9},
+            "gpu_launches": None, "clocks": cs.summary()}
+
+
 # DRAM traffic of one GEMM launch (dram__bytes_read.sum + dram__bytes_write.sum, one ncu capture; see profiles/)
 GEMM_TRAFFIC_BYTES = None
 
@@ -368,7 +456,7 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--workload", default=os.environ.get("MXFP4_BENCH_WORKLOAD", "gemm"), choices=["quantize", "gemm"])
+    ap.add_argument("--workload", default=os.environ.get("MXFP4_BENCH_WORKLOAD", "gemm"), choices=["quantize", "gemm", "stack", "decode"])
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
@@ -394,9 +482,11 @@ def main():
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device (the product has no CPU path); use --impl reference for the CPU baseline")
     rank, world, local = dist_setup(args.gpus)
-    res = (run_gemm if args.workload == "gemm" else run_quantize)(args, rank, world, local)
+    res = {"gemm": run_gemm, "quantize": run_quantize, "stack": run_stack, "decode": run_decode}[args.workload](args, rank, world, local)
     res.update({"n_gpus": world, "steps": args.steps, "warmup": args.warmup, "higher_is_better": True, "scaling": "weak",
                 "vs_baseline": None, "data": "synthetic"})
+    if "scaling_note" in res:
+        res["scaling"] = res.pop("scaling_note")
     if rank == 0:
         print(json.dumps(res))
     if world > 1:

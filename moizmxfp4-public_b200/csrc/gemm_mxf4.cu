@@ -147,7 +147,8 @@ struct Cfg {
     static constexpr int kBudget = 227 * 1024 - 1024 /*alignment*/ - 512 /*barriers*/ - kEpiBytes;
     static constexpr int kStages = (kBudget / kStageBytes) < 8 ? (kBudget / kStageBytes) : 8;
     static constexpr int kSmemBytes = kStages * kStageBytes + kEpiBytes + 1024 + 512;
-    static constexpr uint32_t kTxBytes = kWBytes + kXBytes + kSfwBytes + kSfxBytes;
+    static constexpr uint32_t kTxBytes = kWBytes + kXBytes;          // operand tiles (full barrier)
+    static constexpr uint32_t kSfTxBytes = kSfwBytes + kSfxBytes;    // scale tiles (their own barrier: they land sooner)
     // tensor-memory columns: two accumulators, then scale factors
     // two accumulators (epilogue of one unit overlaps the MMAs of the next) when they fit beside the scale factors
     static constexpr int kAccBufs = BN <= 192 ? 2 : 1;
@@ -208,11 +209,14 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_mxf4_kernel(const __grid_con
     const uint32_t bars = base + C::kStages * C::kStageBytes + C::kEpiBytes;
     auto full_bar = [&](int s) { return bars + 8u * s; };
     auto empty_bar = [&](int s) { return bars + 8u * (C::kStages + s); };
-    auto corr_bar = [&](int s) { return bars + 8u * (2 * C::kStages + s); };
-    auto sf_bar = [&](int s) { return bars + 8u * (3 * C::kStages + s); };
-    auto acc_full_bar = [&](int b) { return bars + 8u * (4 * C::kStages + b); };
-    auto acc_empty_bar = [&](int b) { return bars + 8u * (4 * C::kStages + 2 + b); };
-    uint8_t* tail = epi_ptr + C::kEpiBytes + 8 * (4 * C::kStages + 4);
+    // everything the MMA thread needs for a stage: correction tile built (4 transform warps, EXACT mode) and scale
+    // factors in tensor memory (copier's commit).  One wait per stage: under load every mbarrier round trip costs the
+    // issuing thread a few hundred cycles.
+    auto ready_bar = [&](int s) { return bars + 8u * (2 * C::kStages + s); };
+    auto sfld_bar = [&](int s) { return bars + 8u * (4 * C::kStages + s); };     // scale tiles have landed in shared memory
+    auto acc_full_bar = [&](int b) { return bars + 8u * (5 * C::kStages + b); };
+    auto acc_empty_bar = [&](int b) { return bars + 8u * (5 * C::kStages + 2 + b); };
+    uint8_t* tail = epi_ptr + C::kEpiBytes + 8 * (5 * C::kStages + 4);
     volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(tail);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tail + 4);
 
@@ -223,8 +227,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_mxf4_kernel(const __grid_con
         for (int s = 0; s < C::kStages; ++s) {
             mbar_init(full_bar(s), 1);
             mbar_init(empty_bar(s), 1);
-            mbar_init(corr_bar(s), 4);
-            mbar_init(sf_bar(s), 1);
+            mbar_init(ready_bar(s), p.exact ? 5 : 1);
+            mbar_init(sfld_bar(s), 1);
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(acc_full_bar(b), 1);
@@ -258,16 +262,17 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_mxf4_kernel(const __grid_con
                     if (!mbar_wait(empty_bar(s), ph ^ 1u, abort_flag)) { ok = false; break; }
                     const uint32_t st = base + s * C::kStageBytes;
                     mbar_expect_tx(full_bar(s), C::kTxBytes);
+                    mbar_expect_tx(sfld_bar(s), C::kSfTxBytes);
                     tma_load_2d(st, &map_w, full_bar(s), ks * kStageKBytes, w.n_tile * kTileW);
                     tma_load_2d(st + C::kOffX, &map_x, full_bar(s), ks * kStageKBytes, m0);
-                    bulk_load(st + C::kOffSfw, p.sfw + ((int64_t)w.n_tile * p.kstages + ks) * 2048, 2048, full_bar(s));
+                    bulk_load(st + C::kOffSfw, p.sfw + ((int64_t)w.n_tile * p.kstages + ks) * 2048, 2048, sfld_bar(s));
 #pragma unroll
                     for (int t = 0; t < C::kXT; ++t) {
                         // 128-row scale groups the tile touches; a second group past the end of the buffer is
                         // replaced by the first (its rows are beyond M and never stored)
                         int64_t grp = m0 / 128 + t;
                         if (grp * 128 >= ((int64_t)p.M + 127) / 128 * 128) grp = m0 / 128;
-                        bulk_load(st + C::kOffSfx + t * 1024, p.sfx + (grp * p.kstages + ks) * 1024, 1024, full_bar(s));
+                        bulk_load(st + C::kOffSfx + t * 1024, p.sfx + (grp * p.kstages + ks) * 1024, 1024, sfld_bar(s));
                     }
                 }
             }
@@ -293,9 +298,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_mxf4_kernel(const __grid_con
                 for (int ks = w.ks0; ks < w.ks1; ++ks, ++it) {
                     const int s = it % C::kStages;
                     const uint32_t ph = (it / C::kStages) & 1;
-                    ok = mbar_wait(full_bar(s), ph, abort_flag);                   // operand tiles have landed
-                    if (ok) ok = mbar_wait(sf_bar(s), ph, abort_flag);              // scale factors are in tensor memory
-                    if (ok && p.exact) ok = mbar_wait(corr_bar(s), ph, abort_flag); // correction tile is built
+                    ok = mbar_wait(ready_bar(s), ph, abort_flag);   // tiles landed, correction built, scales in tensor memory
                     if (!ok) break;
                     tc_fence_after();
                     const uint32_t st = base + s * C::kStageBytes;
@@ -344,7 +347,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_mxf4_kernel(const __grid_con
                     for (int j = 0; j < C::kWBytes / 16 / 128; ++j) dst[j * 128 + t] = v[j];   // same offset in and out: the swizzle is preserved
                     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // make the writes visible to the tensor core
                     __syncwarp();
-                    if (lane == 0) mbar_arrive(corr_bar(s));
+                    if (lane == 0) mbar_arrive(ready_bar(s));
                 }
             }
         }
@@ -362,7 +365,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_mxf4_kernel(const __grid_con
                 for (int ks = w.ks0; ks < w.ks1; ++ks, ++it) {
                     const int s = it % C::kStages;
                     const uint32_t ph = (it / C::kStages) & 1;
-                    ok = mbar_wait(full_bar(s), ph, abort_flag);
+                    ok = mbar_wait(sfld_bar(s), ph, abort_flag);
+                    if (ok) ok = mbar_wait(full_bar(s), ph, abort_flag);   // so that "ready" also implies the operand tiles
                     if (!ok) break;
                     tc_fence_after();
                     const uint32_t st = base + s * C::kStageBytes;
@@ -375,7 +379,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_mxf4_kernel(const __grid_con
                         for (int t = 0; t < C::kXT; ++t)
                             tc_cp_sf(sft + C::kColSfx + 4 * C::kXT * g + 4 * t, desc_sf(st + C::kOffSfx + 1024 * t + 512 * g));
                     }
-                    tc_commit(sf_bar(s));
+                    tc_commit(ready_bar(s));
                 }
             }
         }

@@ -1,0 +1,64 @@
+"""Tensor-parallel MXLinear layers on real GPUs (needs >= 2 devices; skipped otherwise): each rank is a child
+process with its own GPU, NCCL for the row-parallel all-reduce.  Column-parallel shards must be bit-identical to
+the matching slice of the unsharded output; the row-parallel sum is compared within the GEMM tolerance."""
+import os
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+pytestmark = pytest.mark.gpu
+
+
+def _worker(rank, world, port, q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        import sys
+        sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+        import conftest
+        from mxfp4 import MXLinear, gemm
+        from mxfp4.parallel import ColumnParallelMXLinear, MXBlockStack, RowParallelMXLinear
+        dev = torch.device("cuda", rank)
+        up = MXLinear(4096, 11008, bias=False)
+        down = MXLinear(11008, 4096, bias=True)
+        up.weight.data = conftest.weight(11008, 4096, 1, True).float()
+        down.weight.data = conftest.weight(4096, 11008, 2, True).float()
+        up.to(dev); down.to(dev)
+        up.quantize(); down.quantize()
+        x = conftest.act(128, 4096, 5).to(dev)
+        h_full = up(x)
+        full = down(torch.relu(h_full))
+        cp = ColumnParallelMXLinear.from_mxlinear(up)
+        rp = RowParallelMXLinear.from_mxlinear(down)
+        h = cp(x)
+        n = 11008 // world
+        ok_col = torch.equal(h, h_full[:, rank * n:(rank + 1) * n])
+        y = rp(torch.relu(h))
+        err = ((y.float() - full.float()).norm() / full.float().norm()).item()
+        stack = MXBlockStack.build(n_layers=2, device=dev)
+        out = stack(conftest.act(16, 4096, 9).to(dev))
+        gemm.check_status()
+        fin = bool(torch.isfinite(out.float()).all().item())
+        ref = [torch.empty_like(out) for _ in range(world)]
+        dist.all_gather(ref, out)
+        same = all(torch.equal(ref[0], r) for r in ref)           # every rank ends with the same replicated activations
+        q.put((rank, ok_col and err < 1e-2 and fin and same, err))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_tensor_parallel_layers_two_gpus():
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 29700 + os.getpid() % 200
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = [q.get(timeout=300) for _ in procs]
+    for p in procs:
+        p.join(timeout=60)
+    assert all(ok for _, ok, _ in res), res
