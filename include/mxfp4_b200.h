@@ -114,7 +114,7 @@ MXFP4_API int mxfp4_act_quantize(const void* x_bf16, int64_t M, int64_t K, int64
  */
 MXFP4_API int mxfp4_prepare_weight_scales(const uint8_t* scales, int64_t N, int64_t K, uint8_t* prepared, void* stream);
 
-/* Workspace of mxfp4_gemm: 256-byte status block + packed activations + blocked activation scales + the
+/* Workspace of mxfp4_gemm: 4 KB control block (status word; rest reserved) + packed activations + blocked activation scales + the
  * float32 partial sums of a K-split (mxfp4_gemm_splitk_bytes; skinny problems, M <= 128, are cut along K so that
  * every SM streams part of the weight; the partials are summed in a fixed order by a second kernel). */
 MXFP4_API int64_t mxfp4_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K, int mode);
@@ -127,8 +127,9 @@ MXFP4_API int64_t mxfp4_gemm_splitk_bytes(int64_t M, int64_t N, int64_t K);
  *   x_bf16         device, [M, K] bf16, row pitch ldx elements
  *   w_packed       device, [N, K/2] uint8, the reference's packed weight, unchanged
  *   w_sf_prepared  device, from mxfp4_prepare_weight_scales
- *   workspace      device, >= mxfp4_gemm_workspace_bytes, 256-byte aligned.  Its first int is a status word that the
- *                  caller zeroes once; a kernel whose bounded wait ran out stores MXFP4_E_TIMEOUT there.
+ *   workspace      device, >= mxfp4_gemm_workspace_bytes, 256-byte aligned.  Its first 4 KB are a control block that the
+ *                  caller zeroes once (not per call): int[0] is a status word -- a kernel whose bounded wait ran out stores
+ *                  MXFP4_E_TIMEOUT there -- and the rest is reserved.
  * K % 32 == 0.  Launches two kernels (activation quantiser, GEMM) on `stream`.
  */
 MXFP4_API int mxfp4_gemm(const void* x_bf16, int64_t ldx, const uint8_t* w_packed, const uint8_t* w_sf_prepared,
@@ -136,11 +137,12 @@ MXFP4_API int mxfp4_gemm(const void* x_bf16, int64_t ldx, const uint8_t* w_packe
                          void* workspace, int64_t workspace_bytes, void* stream);
 
 /* The GEMM alone, on activations already quantised by mxfp4_act_quantize.  splitk_workspace (16-byte aligned,
- * >= mxfp4_gemm_splitk_bytes) may be NULL: the K-split is then not used.  status_dev may be NULL. */
+ * >= mxfp4_gemm_splitk_bytes) may be NULL: the K-split is then not used.  control_block: NULL, or 4 KB of device memory
+ * zeroed once, laid out like the first 4 KB of mxfp4_gemm's workspace (int[0] receives MXFP4_E_TIMEOUT). */
 MXFP4_API int mxfp4_gemm_prequantized(const uint8_t* a_packed, const uint8_t* a_sf_blocked, const uint8_t* w_packed,
                                       const uint8_t* w_sf_prepared, const void* bias_bf16, void* out_bf16, int64_t ldo,
                                       int64_t M, int64_t N, int64_t K, int mode, void* splitk_workspace,
-                                      int64_t splitk_bytes, int* status_dev, void* stream);
+                                      int64_t splitk_bytes, int* control_block, void* stream);
 
 /*
  * mxfp4_gemm without any workspace argument and without any device allocation.  It has no counterpart in the

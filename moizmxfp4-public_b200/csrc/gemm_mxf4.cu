@@ -647,15 +647,18 @@ extern "C" int64_t mxfp4_gemm_splitk_bytes(int64_t M, int64_t N, int64_t K) {
 extern "C" int64_t mxfp4_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K, int mode) {
     (void)mode;
     if (M <= 0 || K <= 0) return 0;
-    // [status word, 256 B] [packed activations M*K/2] [blocked activation scales] [K-split partial sums]
-    return 256 + mxfp4::align_up(M * (K / 2), 256) + mxfp4::align_up(mxfp4_act_scales_bytes(M, K), 256) + mxfp4_gemm_splitk_bytes(M, N, K);
+    // [control block, 4 KB: status word + reserved] [packed activations M*K/2] [blocked activation scales] [K-split partial sums]
+    return 4096 + mxfp4::align_up(M * (K / 2), 256) + mxfp4::align_up(mxfp4_act_scales_bytes(M, K), 256) + mxfp4_gemm_splitk_bytes(M, N, K);
 }
 
-extern "C" int mxfp4_gemm_prequantized(const uint8_t* a_packed, const uint8_t* a_sf_blocked, const uint8_t* w_packed,
-                                       const uint8_t* w_sf_prepared, const void* bias_bf16, void* out_bf16, int64_t ldo, int64_t M,
-                                       int64_t N, int64_t K, int mode, void* splitk_workspace, int64_t splitk_bytes, int* status_dev,
-                                       void* stream) {
-    using namespace mxfp4;
+namespace mxfp4 {
+namespace {
+constexpr int kControlBytes = 4096;     // control block: int[0] = status word, the rest is reserved
+constexpr int kCounterOffset = 64;
+
+int gemm_run(const uint8_t* a_packed, const uint8_t* a_sf_blocked, const uint8_t* w_packed, const uint8_t* w_sf_prepared,
+             const void* bias_bf16, void* out_bf16, int64_t ldo, int64_t M, int64_t N, int64_t K, int mode, void* splitk_workspace,
+             int64_t splitk_bytes, int* status_dev, int* counters, void* stream) {
     if (M < 0 || N < 0 || K < 0) { set_error("mxfp4_gemm: negative size"); return MXFP4_E_SHAPE; }
     if (M == 0 || N == 0) return MXFP4_OK;
     if (K == 0 || K % 32) { set_error("mxfp4_gemm: K=%lld must be a positive multiple of 32", (long long)K); return MXFP4_E_SHAPE; }
@@ -685,6 +688,7 @@ extern "C" int mxfp4_gemm_prequantized(const uint8_t* a_packed, const uint8_t* a
         p.partial = (float*)splitk_workspace;
     }
     p.exact = mode == MXFP4_GEMM_EXACT; p.status = status_dev;
+    (void)counters;
     cudaStream_t st = (cudaStream_t)stream;
     switch (bn) {
         case 32: rc = launch_gemm<32>(mw, mx, p, st); break;
@@ -704,6 +708,16 @@ extern "C" int mxfp4_gemm_prequantized(const uint8_t* a_packed, const uint8_t* a
     }
     return MXFP4_OK;
 }
+}  // namespace
+}  // namespace mxfp4
+
+extern "C" int mxfp4_gemm_prequantized(const uint8_t* a_packed, const uint8_t* a_sf_blocked, const uint8_t* w_packed,
+                                       const uint8_t* w_sf_prepared, const void* bias_bf16, void* out_bf16, int64_t ldo, int64_t M,
+                                       int64_t N, int64_t K, int mode, void* splitk_workspace, int64_t splitk_bytes, int* control_block,
+                                       void* stream) {
+    return mxfp4::gemm_run(a_packed, a_sf_blocked, w_packed, w_sf_prepared, bias_bf16, out_bf16, ldo, M, N, K, mode, splitk_workspace,
+                           splitk_bytes, control_block, control_block ? control_block + mxfp4::kCounterOffset : nullptr, stream);
+}
 
 extern "C" int mxfp4_gemm(const void* x_bf16, int64_t ldx, const uint8_t* w_packed, const uint8_t* w_sf_prepared, const void* bias_bf16,
                           void* out_bf16, int64_t ldo, int64_t M, int64_t N, int64_t K, int mode, void* workspace,
@@ -720,13 +734,13 @@ extern "C" int mxfp4_gemm(const void* x_bf16, int64_t ldx, const uint8_t* w_pack
     if ((uintptr_t)workspace % 256) { set_error("mxfp4_gemm: workspace must be 256-byte aligned"); return MXFP4_E_ALIGN; }
     uint8_t* ws = (uint8_t*)workspace;
     int* status = (int*)ws;
-    uint8_t* a_packed = ws + 256;
+    uint8_t* a_packed = ws + kControlBytes;
     uint8_t* a_sf = a_packed + align_up(M * (K / 2), 256);
     uint8_t* partial = a_sf + align_up(mxfp4_act_scales_bytes(M, K), 256);
     int rc = mxfp4_act_quantize(x_bf16, M, K, ldx, a_packed, a_sf, stream);
     if (rc) return rc;
-    return mxfp4_gemm_prequantized(a_packed, a_sf, w_packed, w_sf_prepared, bias_bf16, out_bf16, ldo, M, N, K, mode, partial,
-                                   mxfp4_gemm_splitk_bytes(M, N, K), status, stream);
+    return gemm_run(a_packed, a_sf, w_packed, w_sf_prepared, bias_bf16, out_bf16, ldo, M, N, K, mode, partial,
+                    mxfp4_gemm_splitk_bytes(M, N, K), status, status + kCounterOffset, stream);
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -757,7 +771,7 @@ extern "C" int mxfp4_gemm_noalloc(const void* x_bf16, int64_t ldx, const uint8_t
     const int64_t act_bytes = align_up(M * (K / 2), 256);
     const int64_t sf_bytes = align_up(mxfp4_act_scales_bytes(M, K), 256);
     const int64_t split_bytes = mxfp4_gemm_splitk_bytes(M, N, K);
-    const int64_t need = act_bytes + sf_bytes + split_bytes;
+    const int64_t need = kControlBytes + act_bytes + sf_bytes + split_bytes;
     if (need > kNoAllocScratchBytes) {
         set_error("mxfp4_gemm_noalloc: M=%lld N=%lld K=%lld needs %lld bytes of scratch, the built-in array holds %lld; "
                   "use mxfp4_gemm with a caller-provided workspace for this size",
@@ -777,11 +791,12 @@ extern "C" int mxfp4_gemm_noalloc(const void* x_bf16, int64_t ldx, const uint8_t
         if (e != cudaSuccess) return cuda_fail(e, "mxfp4_gemm_noalloc: cudaGetSymbolAddress");
         scratch_addr[dev] = (unsigned char*)ptr;
     }
-    uint8_t* a_packed = scratch_addr[dev];
+    int* counters = (int*)scratch_addr[dev];            // reserved control block
+    uint8_t* a_packed = scratch_addr[dev] + kControlBytes;
     uint8_t* a_sf = a_packed + act_bytes;
     uint8_t* partial = a_sf + sf_bytes;
     int rc = mxfp4_act_quantize(x_bf16, M, K, ldx, a_packed, a_sf, stream);
     if (rc) return rc;
-    return mxfp4_gemm_prequantized(a_packed, a_sf, w_packed, w_sf_prepared, bias_bf16, out_bf16, ldo, M, N, K, mode,
-                                   split_bytes ? partial : nullptr, split_bytes, status_dev, stream);
+    return gemm_run(a_packed, a_sf, w_packed, w_sf_prepared, bias_bf16, out_bf16, ldo, M, N, K, mode,
+                    split_bytes ? partial : nullptr, split_bytes, status_dev, counters, stream);
 }

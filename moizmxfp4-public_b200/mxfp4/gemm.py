@@ -21,6 +21,11 @@ _lock = threading.RLock()
 _prepared = OrderedDict()        # id(scale tensor) -> (weakref, version, (N, K, ptr), prepared scale tensor)
 _PREPARED_MAX = 4096
 _workspaces = {}                 # (device index, stream) -> uint8 tensor
+_last_act = {}                   # (device index, stream) -> (activation pointer, M, K, workspace pointer) of the last quantisation
+
+
+def _align(v, a):
+    return (v + a - 1) // a * a
 
 
 def set_gemm_mode(mode: str):
@@ -75,6 +80,7 @@ def _workspace(device: torch.device, nbytes: int) -> torch.Tensor:
     if ws is None or ws.numel() < nbytes:
         ws = torch.zeros(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)   # zeroed: the status word starts clear
         _workspaces[key] = ws
+        _last_act.pop(key, None)
     return ws
 
 
@@ -105,7 +111,7 @@ def act_quantize(x: torch.Tensor):
 
 
 def quant_matmul_2d(input: torch.Tensor, packed_weight: torch.Tensor, weight_scales: torch.Tensor,
-                    bias: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+                    bias: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None, reuse_act: bool = False) -> torch.Tensor:
     """[M,K] x packed [N,K/2] (+bias) -> [M,N]; argument contract of the reference's quant_matmul
     (src/mxfp4/fused_kernels.py:160-207: 2-D tensors, K_packed*2 == K)."""
     assert input.dim() == 2, "Input must be 2D [M, K]"
@@ -138,10 +144,25 @@ def quant_matmul_2d(input: torch.Tensor, packed_weight: torch.Tensor, weight_sca
         return out.to(in_dtype)
     nbytes = L.mxfp4_gemm_workspace_bytes(M, N, K, _mode)
     ws = _workspace(dev, nbytes)
+    ws_key = (dev.index, torch.cuda.current_stream(dev).cuda_stream)
+    a_off = 4096
+    sf_off = a_off + _align(M * (K // 2), 256)
+    part_off = sf_off + _align(L.mxfp4_act_scales_bytes(M, K), 256)
+    last = _last_act.get(ws_key)
+    reuse = reuse_act and last == (x.data_ptr(), M, K, ws.data_ptr())
     with torch.cuda.device(dev):
-        _capi.check(L.mxfp4_gemm(x.data_ptr(), x.stride(0), pw.data_ptr(), sfw.data_ptr(), None if b is None else b.data_ptr(),
-                                 out.data_ptr(), out.stride(0), M, N, K, _mode, ws.data_ptr(), ws.numel(), _capi.stream_ptr(dev)),
-                    "mxfp4_gemm")
+        if reuse:
+            # the caller vouches that the previous GEMM on this stream quantised these same activations (q/k/v and
+            # gate/up share their input); the workspace still holds their MXFP4 form
+            _capi.check(L.mxfp4_gemm_prequantized(ws.data_ptr() + a_off, ws.data_ptr() + sf_off, pw.data_ptr(), sfw.data_ptr(),
+                                                  None if b is None else b.data_ptr(), out.data_ptr(), out.stride(0), M, N, K, _mode,
+                                                  ws.data_ptr() + part_off, ws.numel() - part_off, ws.data_ptr(), _capi.stream_ptr(dev)),
+                        "mxfp4_gemm_prequantized")
+        else:
+            _capi.check(L.mxfp4_gemm(x.data_ptr(), x.stride(0), pw.data_ptr(), sfw.data_ptr(), None if b is None else b.data_ptr(),
+                                     out.data_ptr(), out.stride(0), M, N, K, _mode, ws.data_ptr(), ws.numel(), _capi.stream_ptr(dev)),
+                        "mxfp4_gemm")
+            _last_act[ws_key] = (x.data_ptr(), M, K, ws.data_ptr())
     return out if in_dtype == torch.bfloat16 else out.to(in_dtype)
 
 
@@ -157,7 +178,7 @@ def _matmul_bf16_scales(input, packed_weight, weight_scales, bias):
 
 
 def mxlinear_forward(input: torch.Tensor, packed_weight: torch.Tensor, weight_scales: torch.Tensor,
-                     bias: Optional[torch.Tensor], in_features: int) -> torch.Tensor:
+                     bias: Optional[torch.Tensor], in_features: int, reuse_act: bool = False) -> torch.Tensor:
     """MXLinear.forward for a quantised layer: any leading dimensions, output in the input's dtype."""
     lead = input.shape[:-1]
     x = input.reshape(-1, input.shape[-1])
@@ -165,5 +186,5 @@ def mxlinear_forward(input: torch.Tensor, packed_weight: torch.Tensor, weight_sc
     if x.shape[-1] != k_pad:
         # the quantiser padded the weight rows to a multiple of the block; padded weight columns meet zeros
         x = torch.nn.functional.pad(x, (0, k_pad - x.shape[-1]))
-    y = quant_matmul_2d(x, packed_weight, weight_scales, bias)
+    y = quant_matmul_2d(x, packed_weight, weight_scales, bias, reuse_act=reuse_act)
     return y.reshape(*lead, packed_weight.shape[0])

@@ -78,8 +78,10 @@ class ColumnParallelMXLinear(_ParallelBase):
         self._load(p, s, b)
         return self
 
-    def forward(self, x: torch.Tensor) -> torch.Tensor:
-        y = _gemm.mxlinear_forward(x, self.packed_weight, self.weight_scales, self.bias, self.in_features)
+    def forward(self, x: torch.Tensor, reuse_act: bool = False) -> torch.Tensor:
+        """reuse_act=True: the previous layer call on this stream had the same input (q/k/v, gate/up); its quantised
+        activations are reused instead of being recomputed."""
+        y = _gemm.mxlinear_forward(x, self.packed_weight, self.weight_scales, self.bias, self.in_features, reuse_act)
         if self.gather_output and self.world > 1:
             parts = [torch.empty_like(y) for _ in range(self.world)]
             dist.all_gather(parts, y.contiguous(), group=self.group)
@@ -156,10 +158,10 @@ class MXBlockStack(nn.Module):
     def forward(self, h: torch.Tensor) -> torch.Tensor:
         for L in self.layers:
             x = self._norm(h)
-            a = L["q"](x) + L["k"](x) + L["v"](x)
+            a = L["q"](x) + L["k"](x, reuse_act=True) + L["v"](x, reuse_act=True)
             h = h + L["o"](a)
             x = self._norm(h)
-            g = torch.nn.functional.silu(L["gate"](x)) * L["up"](x)
+            g = torch.nn.functional.silu(L["gate"](x)) * L["up"](x, reuse_act=True)
             h = h + L["down"](g)
         return h
 

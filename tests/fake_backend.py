@@ -14,14 +14,14 @@ def _dequantize(packed, scales, block_size, out_dtype=torch.float32):
     return oracle.dequantize(packed, scales, block_size).to(out_dtype)
 
 
-def _matmul(x, packed, scales, bias=None, out=None):
+def _matmul(x, packed, scales, bias=None, out=None, reuse_act=False):
     y = oracle.matmul_operand_matched(x.detach().to(torch.bfloat16), packed, scales, None).to(torch.bfloat16)
     if bias is not None:
         y = (y.float() + bias.detach().float()).to(torch.bfloat16)
     return y.to(x.dtype)
 
 
-def _forward(x, packed, scales, bias, in_features):
+def _forward(x, packed, scales, bias, in_features, reuse_act=False):
     lead = x.shape[:-1]
     x2 = x.reshape(-1, x.shape[-1])
     k_pad = packed.shape[-1] * 2

@@ -139,3 +139,20 @@ def test_bf16_scale_weights_take_the_dense_side_path():
     y = quant_matmul(x.cuda(), op.cuda(), os_.cuda())
     ref = (x.float() @ oracle.dequantize(op, os_).to(torch.bfloat16).float().T)
     assert rel_fro(y.float().cpu(), ref) < 5e-3
+
+
+def test_reused_activation_quantisation_gives_identical_results():
+    """q/k/v-style calls: the second GEMM on the same input may skip the activation quantiser."""
+    from mxfp4 import gemm
+    x = act(48, 1024, 3).cuda()
+    p1, s1 = oracle.quantize(weight(256, 1024, 5, True))
+    p2, s2 = oracle.quantize(weight(384, 1024, 6, True))
+    p1, s1, p2, s2 = p1.cuda(), s1.cuda(), p2.cuda(), s2.cuda()
+    ref2 = gemm.quant_matmul_2d(x, p2, s2)
+    gemm.quant_matmul_2d(x, p1, s1)
+    got2 = gemm.quant_matmul_2d(x, p2, s2, reuse_act=True)
+    assert torch.equal(got2, ref2)
+    other = act(48, 1024, 4).cuda()
+    got_other = gemm.quant_matmul_2d(other, p2, s2, reuse_act=True)       # different tensor: the flag is ignored, not trusted
+    assert torch.equal(got_other, gemm.quant_matmul_2d(other, p2, s2))
+    gemm.check_status()
