@@ -31,6 +31,9 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 sys.path.insert(0, os.path.join(ROOT, "moizmxfp4-public_b200"))
 
+if os.environ.get("NCCL_DEBUG", "").upper() == "VERSION":     # keep NCCL's version banner off stdout: one JSON line only
+    os.environ["NCCL_DEBUG"] = "WARN"
+
 import torch  # noqa: E402
 
 QUANT_BYTES_PER_ELEM = 2.0 + 0.5 + 1.0 / 32.0
