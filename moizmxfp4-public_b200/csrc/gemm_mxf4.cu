@@ -29,7 +29,7 @@ namespace {
 constexpr int kTileW = 128;         // weight rows per CTA (MMA M)
 constexpr int kStageK = 256;        // elements of K per pipeline stage
 constexpr int kStageKBytes = 128;   // bytes per row per stage
-constexpr uint32_t kSpinLimit = 1u << 22;
+constexpr long long kWaitLimitCycles = 2000000000ll;   // about one second: a wait that long has failed
 
 // ---------------------------------------------------------------- PTX wrappers
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -57,11 +57,14 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 // Bounded wait.  Returns false (and raises the CTA's abort flag) when the limit is reached or another
 // role has already given up.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
-    for (uint32_t it = 0; it < kSpinLimit; ++it) {
+    // try_wait suspends the thread in hardware until the phase completes or a short time limit passes, so a plain
+    // retry loop wakes up with the lowest latency; the abort flag and the bound are looked at every 64 retries.
+    const long long t0 = clock64();
+    for (uint32_t it = 1;; ++it) {
         if (mbar_try_wait(bar, parity)) return true;
-        if (it > 32) {
-            __nanosleep(64);
+        if ((it & 63u) == 0) {
             if (*abort_flag) return false;
+            if (clock64() - t0 > kWaitLimitCycles) break;
         }
     }
     *abort_flag = 1;
@@ -366,7 +369,6 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_mxf4_kernel(const __grid_con
                     const int s = it % C::kStages;
                     const uint32_t ph = (it / C::kStages) & 1;
                     ok = mbar_wait(sfld_bar(s), ph, abort_flag);
-                    if (ok) ok = mbar_wait(full_bar(s), ph, abort_flag);   // so that "ready" also implies the operand tiles
                     if (!ok) break;
                     tc_fence_after();
                     const uint32_t st = base + s * C::kStageBytes;
@@ -379,6 +381,9 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_mxf4_kernel(const __grid_con
                         for (int t = 0; t < C::kXT; ++t)
                             tc_cp_sf(sft + C::kColSfx + 4 * C::kXT * g + 4 * t, desc_sf(st + C::kOffSfx + 1024 * t + 512 * g));
                     }
+                    // the copies are under way; "ready" must also imply that the operand tiles have landed
+                    ok = mbar_wait(full_bar(s), ph, abort_flag);
+                    if (!ok) break;
                     tc_commit(ready_bar(s));
                 }
             }
@@ -613,8 +618,8 @@ int pick_bn(int64_t M) {
     if (M <= 64) return 64;
     if (M <= 128) return 128;
     const int64_t pad256 = (M + 255) / 256 * 256, pad192 = (M + 191) / 192 * 192;
-    if (pad256 * 100 <= M * 104) return 256;      // widest tile: fewest shared-memory bytes per MAC
-    return pad192 * 100 <= M * 104 ? 192 : 128;
+    if (pad192 * 100 <= M * 104) return 192;      // two accumulators fit: the epilogue overlaps the next unit's MMAs
+    return pad256 * 100 <= M * 104 ? 256 : 128;
 }
 
 // Number of K ranges.  Skinny problems have fewer tiles than SMs; cutting K spreads the weight stream over
