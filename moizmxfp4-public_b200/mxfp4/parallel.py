@@ -132,9 +132,11 @@ class MXBlockStack(nn.Module):
         return (h.float() * torch.rsqrt(h.float().pow(2).mean(-1, keepdim=True) + 1e-6)).to(h.dtype)
 
     @classmethod
-    def build(cls, n_layers=32, hidden=4096, inter=11008, device="cuda", group=None, seed=0, block_size=32):
+    def build(cls, n_layers=32, hidden=4096, inter=11008, device="cuda", group=None, seed=0, block_size=32, fuse=True):
         """Random-init N(0, 0.02) bf16 weights, quantised and sharded for this rank.  Every rank draws the
-        same full matrices from the same CPU generator (seed = layer*7 + j) and keeps its slice."""
+        same full matrices from the same CPU generator (seed = layer*7 + j) and keeps its slice.
+        fuse=True stores q|k|v and gate|up as one column-parallel layer each (their packed rows concatenated,
+        which changes no byte of any of them): one GEMM launch instead of three / two."""
         world, rank = _group_info(group)
         layers = []
         for li in range(n_layers):
@@ -152,16 +154,31 @@ class MXBlockStack(nn.Module):
                 par = (ColumnParallelMXLinear if col else RowParallelMXLinear)(k, n, group)
                 par._load(lin.packed_weight, lin.weight_scales, None)
                 mods[name] = par
+            if fuse:
+                for fused, parts in (("qkv", ("q", "k", "v")), ("gateup", ("gate", "up"))):
+                    par = ColumnParallelMXLinear(mods[parts[0]].in_features, sum(mods[p].out_features for p in parts), group)
+                    par._load(torch.cat([mods[p].packed_weight for p in parts], 0), torch.cat([mods[p].weight_scales for p in parts], 0), None)
+                    for p in parts:
+                        del mods[p]
+                    mods[fused] = par
             layers.append(nn.ModuleDict(mods))
         return cls(layers)
 
     def forward(self, h: torch.Tensor) -> torch.Tensor:
         for L in self.layers:
             x = self._norm(h)
-            a = L["q"](x) + L["k"](x, reuse_act=True) + L["v"](x, reuse_act=True)
+            if "qkv" in L:
+                q, k, v = L["qkv"](x).chunk(3, dim=-1)
+                a = q + k + v
+            else:
+                a = L["q"](x) + L["k"](x, reuse_act=True) + L["v"](x, reuse_act=True)
             h = h + L["o"](a)
             x = self._norm(h)
-            g = torch.nn.functional.silu(L["gate"](x)) * L["up"](x, reuse_act=True)
+            if "gateup" in L:
+                gate, up = L["gateup"](x).chunk(2, dim=-1)
+                g = torch.nn.functional.silu(gate) * up
+            else:
+                g = torch.nn.functional.silu(L["gate"](x)) * L["up"](x, reuse_act=True)
             h = h + L["down"](g)
         return h
 

@@ -156,3 +156,67 @@ def test_reused_activation_quantisation_gives_identical_results():
     got_other = gemm.quant_matmul_2d(other, p2, s2, reuse_act=True)       # different tensor: the flag is ignored, not trusted
     assert torch.equal(got_other, gemm.quant_matmul_2d(other, p2, s2))
     gemm.check_status()
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 4096, 32768), (16, 4096, 32768), (1, 4096, 65536), (16, 4096, 65536)])
+def test_extreme_k_skinny_gemm(M, N, K):
+    """Skinny GEMMs with very long K (weights with 0.1 % x50 outliers): the K-split path."""
+    from mxfp4 import gemm, quant_matmul
+    w = weight(N, K, 1, True)
+    x = act(M, K, 1000 + M)
+    op, os_ = oracle.quantize(w)
+    y = quant_matmul(x.cuda(), op.cuda(), os_.cuda())
+    gemm.check_status()
+    ref = oracle.matmul_operand_matched(x, op, os_)
+    err = rel_fro(y.float().cpu(), ref)
+    print(f"M={M} N={N} K={K}: rel_fro={err:.3e} max_abs={(y.float().cpu() - ref).abs().max().item():.4g}")
+    assert err <= TOL
+
+
+@pytest.mark.parametrize("name,N,K,split", [("q/o column shard", 8192, 8192, 0), ("o row shard", 8192, 8192, 1), ("kv column shard", 1024, 8192, 0),
+                                            ("gate/up column shard", 28672, 8192, 0), ("down row shard", 8192, 28672, 1)])
+def test_llama70b_layer_shapes_sharded_8_way(name, N, K, split):
+    """Llama-2-70B layer shapes, one of eight tensor-parallel shards each: the shard of the quantised weight is
+    bit-identical to quantising the shard, and the GEMM on it meets the tolerance."""
+    from mxfp4 import gemm, quant_matmul
+    from mxfp4.parallel import shard_quantized
+    from mxfp4.quantizer import MXFP4Quantizer
+    rank, world = 3, 8
+    g = torch.Generator().manual_seed(N + K)
+    n_s, k_s = (N // world, K) if split == 0 else (N, K // world)
+    # build only the shard (the full 28672x8192 matrix is not needed): rows/columns [rank*size, (rank+1)*size)
+    w_shard = (torch.randn(n_s, k_s, generator=g) * 0.02).to(torch.bfloat16)
+    q = MXFP4Quantizer(32, "e8m0")
+    p_dev, s_dev = q.quantize(w_shard.cuda())
+    op, os_ = oracle.quantize(w_shard)
+    assert torch.equal(p_dev.cpu(), op) and torch.equal(s_dev.cpu(), os_)
+    # slicing a larger quantised matrix gives the same bytes (checked on a 2-shard neighbourhood to bound memory)
+    if split == 0:
+        big = torch.cat([w_shard, w_shard.flip(0)], 0)
+        pb, sb = oracle.quantize(big)
+        ps, ss = shard_quantized(pb, sb, 0, 2, 0)
+    else:
+        big = torch.cat([w_shard, w_shard.flip(1)], 1)
+        pb, sb = oracle.quantize(big)
+        ps, ss = shard_quantized(pb, sb, 1, 2, 0)
+    assert torch.equal(ps, op) and torch.equal(ss, os_)
+    x = act(128, k_s, 7)
+    y = quant_matmul(x.cuda(), p_dev, s_dev)
+    gemm.check_status()
+    ref = oracle.matmul_operand_matched(x, op, os_)
+    err = rel_fro(y.float().cpu(), ref)
+    print(f"{name}: shard [{n_s},{k_s}] rel_fro={err:.3e}")
+    assert err <= TOL
+
+
+def test_block_stack_fused_projections_bit_identical():
+    """Storing q|k|v and gate|up as one layer each (fewer launches) must not change any output bit."""
+    from mxfp4 import gemm
+    from mxfp4.parallel import MXBlockStack
+    x = act(40, 512, 11).cuda()
+    fused = MXBlockStack.build(n_layers=2, hidden=512, inter=1536, device="cuda", fuse=True)
+    plain = MXBlockStack.build(n_layers=2, hidden=512, inter=1536, device="cuda", fuse=False)
+    with torch.no_grad():
+        a, b = fused(x), plain(x)
+    gemm.check_status()
+    assert torch.isfinite(a.float()).all() and torch.equal(a, b)
