@@ -659,11 +659,10 @@ extern "C" int64_t mxfp4_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K, i
 namespace mxfp4 {
 namespace {
 constexpr int kControlBytes = 4096;     // control block: int[0] = status word, the rest is reserved
-constexpr int kCounterOffset = 64;
 
 int gemm_run(const uint8_t* a_packed, const uint8_t* a_sf_blocked, const uint8_t* w_packed, const uint8_t* w_sf_prepared,
              const void* bias_bf16, void* out_bf16, int64_t ldo, int64_t M, int64_t N, int64_t K, int mode, void* splitk_workspace,
-             int64_t splitk_bytes, int* status_dev, int* counters, void* stream) {
+             int64_t splitk_bytes, int* status_dev, void* stream) {
     if (M < 0 || N < 0 || K < 0) { set_error("mxfp4_gemm: negative size"); return MXFP4_E_SHAPE; }
     if (M == 0 || N == 0) return MXFP4_OK;
     if (K == 0 || K % 32) { set_error("mxfp4_gemm: K=%lld must be a positive multiple of 32", (long long)K); return MXFP4_E_SHAPE; }
@@ -693,7 +692,6 @@ int gemm_run(const uint8_t* a_packed, const uint8_t* a_sf_blocked, const uint8_t
         p.partial = (float*)splitk_workspace;
     }
     p.exact = mode == MXFP4_GEMM_EXACT; p.status = status_dev;
-    (void)counters;
     cudaStream_t st = (cudaStream_t)stream;
     switch (bn) {
         case 32: rc = launch_gemm<32>(mw, mx, p, st); break;
@@ -721,7 +719,7 @@ extern "C" int mxfp4_gemm_prequantized(const uint8_t* a_packed, const uint8_t* a
                                        int64_t N, int64_t K, int mode, void* splitk_workspace, int64_t splitk_bytes, int* control_block,
                                        void* stream) {
     return mxfp4::gemm_run(a_packed, a_sf_blocked, w_packed, w_sf_prepared, bias_bf16, out_bf16, ldo, M, N, K, mode, splitk_workspace,
-                           splitk_bytes, control_block, control_block ? control_block + mxfp4::kCounterOffset : nullptr, stream);
+                           splitk_bytes, control_block, stream);
 }
 
 extern "C" int mxfp4_gemm(const void* x_bf16, int64_t ldx, const uint8_t* w_packed, const uint8_t* w_sf_prepared, const void* bias_bf16,
@@ -745,7 +743,7 @@ extern "C" int mxfp4_gemm(const void* x_bf16, int64_t ldx, const uint8_t* w_pack
     int rc = mxfp4_act_quantize(x_bf16, M, K, ldx, a_packed, a_sf, stream);
     if (rc) return rc;
     return gemm_run(a_packed, a_sf, w_packed, w_sf_prepared, bias_bf16, out_bf16, ldo, M, N, K, mode, partial,
-                    mxfp4_gemm_splitk_bytes(M, N, K), status, status + kCounterOffset, stream);
+                    mxfp4_gemm_splitk_bytes(M, N, K), status, stream);
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -796,12 +794,11 @@ extern "C" int mxfp4_gemm_noalloc(const void* x_bf16, int64_t ldx, const uint8_t
         if (e != cudaSuccess) return cuda_fail(e, "mxfp4_gemm_noalloc: cudaGetSymbolAddress");
         scratch_addr[dev] = (unsigned char*)ptr;
     }
-    int* counters = (int*)scratch_addr[dev];            // reserved control block
     uint8_t* a_packed = scratch_addr[dev] + kControlBytes;
     uint8_t* a_sf = a_packed + act_bytes;
     uint8_t* partial = a_sf + sf_bytes;
     int rc = mxfp4_act_quantize(x_bf16, M, K, ldx, a_packed, a_sf, stream);
     if (rc) return rc;
     return gemm_run(a_packed, a_sf, w_packed, w_sf_prepared, bias_bf16, out_bf16, ldo, M, N, K, mode,
-                    split_bytes ? partial : nullptr, split_bytes, status_dev, counters, stream);
+                    split_bytes ? partial : nullptr, split_bytes, status_dev, stream);
 }
