@@ -4,6 +4,7 @@ There is no CPU implementation and no alternative GPU path: if the shared librar
 tensor is not on a CUDA device, the call raises.  Build the library with
 ``python moizmxfp4-public_b200/build.py``.
 """
+import contextlib
 import ctypes
 import os
 
@@ -83,6 +84,16 @@ def require_cuda(t: torch.Tensor, what: str):
                            "the sm_100a backend is the only backend and there is no CPU fallback")
 
 
+_NULL_CTX = contextlib.nullcontext()
+
+
+def on_device(device):
+    """Context that makes `device` current; free when it already is (the common case)."""
+    if torch.cuda.current_device() == device.index:
+        return _NULL_CTX
+    return torch.cuda.device(device)
+
+
 def stream_ptr(device) -> int:
     return torch.cuda.current_stream(device).cuda_stream
 
@@ -117,7 +128,7 @@ def quantize(x: torch.Tensor, block_size: int, scale_format: str):
     nblk = (cols + block_size - 1) // block_size
     packed = torch.empty(lead + (nblk * block_size // 2,), dtype=torch.uint8, device=x.device)
     scales = torch.empty(lead + (nblk,), dtype=torch.uint8 if scale_format == "e8m0" else torch.bfloat16, device=x.device)
-    with torch.cuda.device(x.device):
+    with on_device(x.device):
         check(L.mxfp4_quantize(x.data_ptr(), DT[x.dtype], rows, cols, ld, block_size, SF[scale_format],
                                packed.data_ptr(), scales.data_ptr(), stream_ptr(x.device)), "mxfp4_quantize")
     return packed, scales
@@ -146,7 +157,7 @@ def dequantize(packed: torch.Tensor, scales: torch.Tensor, block_size: int, out_
     if scales.numel() * block_size != rows * cols_pad:
         raise RuntimeError(f"mxfp4: shape mismatch: {scales.numel()} scales x block {block_size} != {rows * cols_pad} elements")
     out = torch.empty(tuple(packed.shape[:-1]) + (cols_pad,), dtype=out_dtype, device=packed.device)
-    with torch.cuda.device(packed.device):
+    with on_device(packed.device):
         check(L.mxfp4_dequantize(packed.data_ptr(), scales.data_ptr(), SF[fmt], rows, cols_pad, block_size,
                                  out.data_ptr(), DT[out_dtype], stream_ptr(packed.device)), "mxfp4_dequantize")
     return out

@@ -57,7 +57,7 @@ def prepared_scales(weight_scales: torch.Tensor, N: int, K: int) -> torch.Tensor
     L = _capi.load()
     ws = weight_scales.contiguous()
     out = torch.empty(L.mxfp4_prepared_scales_bytes(N, K), dtype=torch.uint8, device=ws.device)
-    with torch.cuda.device(ws.device):
+    with _capi.on_device(ws.device):
         _capi.check(L.mxfp4_prepare_weight_scales(ws.data_ptr(), N, K, out.data_ptr(), _capi.stream_ptr(ws.device)),
                     "mxfp4_prepare_weight_scales")
 
@@ -104,7 +104,7 @@ def act_quantize(x: torch.Tensor):
     M, K = x.shape
     packed = torch.empty(M, K // 2, dtype=torch.uint8, device=x.device)
     sf = torch.empty(L.mxfp4_act_scales_bytes(M, K), dtype=torch.uint8, device=x.device)
-    with torch.cuda.device(x.device):
+    with _capi.on_device(x.device):
         _capi.check(L.mxfp4_act_quantize(x.data_ptr(), M, K, K, packed.data_ptr(), sf.data_ptr(), _capi.stream_ptr(x.device)),
                     "mxfp4_act_quantize")
     return packed, sf
@@ -150,7 +150,7 @@ def quant_matmul_2d(input: torch.Tensor, packed_weight: torch.Tensor, weight_sca
     part_off = sf_off + _align(L.mxfp4_act_scales_bytes(M, K), 256)
     last = _last_act.get(ws_key)
     reuse = reuse_act and last == (x.data_ptr(), M, K, ws.data_ptr())
-    with torch.cuda.device(dev):
+    with _capi.on_device(dev):
         if reuse:
             # the caller vouches that the previous GEMM on this stream quantised these same activations (q/k/v and
             # gate/up share their input); the workspace still holds their MXFP4 form
