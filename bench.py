@@ -204,6 +204,9 @@ def run_quantize(args, rank, world, local):
     pk = peaks()
     roof = {"bound": "hbm", "kernel": "quantize_bf16_b32_kernel [11008x4096]", "achieved": k_bytes / (k_ms * 1e-3) / 1e9,
             "peak": pk["hbm_gbs"], "unit": "GB/s", "peak_source": pk["source"], "traffic": None}
+    # DRAM traffic per launch: one ncu capture of this kernel on a 16384x8192 tensor read+wrote 324.08 MB for 339.74 MB of
+    # algorithmic bytes (the rest of the output was still in L2); traffic is proportional to the element count
+    roof["traffic"] = 324.08 / 339.74 * elems * QUANT_BYTES_PER_ELEM / len(LAYER_SHAPES)
     if graphed:
         # all launches of a step are this one kernel: mean launch duration over the timed region = step time / 7
         roof.update({"kernel": "quantize_bf16_b32_kernel (mean over the 7 launches of a step, timed region)",
@@ -498,7 +501,7 @@ def run_decode(args, rank, world, local):
 
 
 # DRAM traffic of one GEMM launch (dram__bytes_read.sum + dram__bytes_write.sum, one ncu capture; see profiles/)
-GEMM_TRAFFIC_BYTES = None
+GEMM_TRAFFIC_BYTES = 43.42e6 + 135.53e6   # read + write, mean of 3 captured launches of the bench shape (1-pass ncu)
 
 
 def main():
