@@ -141,15 +141,16 @@ struct Cfg {
     static constexpr int kXBytes = BN * kStageKBytes;
     static constexpr int kSfwBytes = 2048;
     static constexpr int kSfxBytes = 1024 * kXT;
-    static constexpr int kOffC = kWBytes;
-    static constexpr int kOffX = 2 * kWBytes;
+    static constexpr int kOffX = kWBytes;
+    static constexpr int kCorrBufs = 2;                            // correction tiles live in a small ring of their own, so that a
+    static constexpr int kCorrBytes = kCorrBufs * kWBytes;         // pipeline slot only holds what TMA delivers (more slots in flight)
     static constexpr int kOffSfw = kOffX + kXBytes;
     static constexpr int kOffSfx = kOffSfw + kSfwBytes;
     static constexpr int kStageBytes = (kOffSfx + kSfxBytes + 1023) / 1024 * 1024;
     static constexpr int kEpiBytes = 4 * 4096;                     // per epilogue warp: 32 x 32 words for the transpose
-    static constexpr int kBudget = 227 * 1024 - 1024 /*alignment*/ - 512 /*barriers*/ - kEpiBytes;
+    static constexpr int kBudget = 227 * 1024 - 1024 /*alignment*/ - 512 /*barriers*/ - kEpiBytes - kCorrBytes;
     static constexpr int kStages = (kBudget / kStageBytes) < 8 ? (kBudget / kStageBytes) : 8;
-    static constexpr int kSmemBytes = kStages * kStageBytes + kEpiBytes + 1024 + 512;
+    static constexpr int kSmemBytes = kStages * kStageBytes + kCorrBytes + kEpiBytes + 1024 + 512;
     static constexpr uint32_t kTxBytes = kWBytes + kXBytes;          // operand tiles (full barrier)
     static constexpr uint32_t kSfTxBytes = kSfwBytes + kSfxBytes;    // scale tiles (their own barrier: they land sooner)
     // tensor-memory columns: two accumulators, then scale factors
@@ -208,8 +209,10 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_mxf4_kernel(const __grid_con
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;                 // stages need 1024-byte alignment (128-byte swizzle)
     uint8_t* base_ptr = smem_raw + (base - raw);
-    uint8_t* epi_ptr = base_ptr + C::kStages * C::kStageBytes;
-    const uint32_t bars = base + C::kStages * C::kStageBytes + C::kEpiBytes;
+    const uint32_t corr_base = base + C::kStages * C::kStageBytes;                 // ring of correction tiles
+    uint8_t* corr_ptr = base_ptr + C::kStages * C::kStageBytes;
+    uint8_t* epi_ptr = corr_ptr + C::kCorrBytes;
+    const uint32_t bars = corr_base + C::kCorrBytes + C::kEpiBytes;
     auto full_bar = [&](int s) { return bars + 8u * s; };
     auto empty_bar = [&](int s) { return bars + 8u * (C::kStages + s); };
     // everything the MMA thread needs for a stage: correction tile built (4 transform warps, EXACT mode) and scale
@@ -217,9 +220,10 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_mxf4_kernel(const __grid_con
     // issuing thread a few hundred cycles.
     auto ready_bar = [&](int s) { return bars + 8u * (2 * C::kStages + s); };
     auto sfld_bar = [&](int s) { return bars + 8u * (4 * C::kStages + s); };     // scale tiles have landed in shared memory
-    auto acc_full_bar = [&](int b) { return bars + 8u * (5 * C::kStages + b); };
-    auto acc_empty_bar = [&](int b) { return bars + 8u * (5 * C::kStages + 2 + b); };
-    uint8_t* tail = epi_ptr + C::kEpiBytes + 8 * (5 * C::kStages + 4);
+    auto corr_empty_bar = [&](int c) { return bars + 8u * (5 * C::kStages + c); };   // MMAs have finished with a correction tile
+    auto acc_full_bar = [&](int b) { return bars + 8u * (5 * C::kStages + C::kCorrBufs + b); };
+    auto acc_empty_bar = [&](int b) { return bars + 8u * (5 * C::kStages + C::kCorrBufs + 2 + b); };
+    uint8_t* tail = epi_ptr + C::kEpiBytes + 8 * (5 * C::kStages + C::kCorrBufs + 4);
     volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(tail);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tail + 4);
 
@@ -233,6 +237,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_mxf4_kernel(const __grid_con
             mbar_init(ready_bar(s), p.exact ? 5 : 1);
             mbar_init(sfld_bar(s), 1);
         }
+        for (int c = 0; c < C::kCorrBufs; ++c) mbar_init(corr_empty_bar(c), 1);
         for (int b = 0; b < 2; ++b) {
             mbar_init(acc_full_bar(b), 1);
             mbar_init(acc_empty_bar(b), 4);
@@ -307,7 +312,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_mxf4_kernel(const __grid_con
                     const uint32_t st = base + s * C::kStageBytes;
                     const uint32_t sft = tmem + s * C::kSfSetCols;       // this stage's scale-factor columns
                     const uint32_t sfx_col = sft + C::kColSfx + sfx_off;
-                    const uint64_t wdesc = desc_sw128(st), cdesc = desc_sw128(st + C::kOffC), xdesc = desc_sw128(st + C::kOffX);
+                    const int cb = it % C::kCorrBufs;                    // correction tile of this stage
+                    const uint64_t wdesc = desc_sw128(st), cdesc = desc_sw128(corr_base + cb * C::kWBytes), xdesc = desc_sw128(st + C::kOffX);
 #pragma unroll
                     for (int kb = 0; kb < 4; ++kb) {
                         const int g = kb >> 1;
@@ -317,7 +323,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_mxf4_kernel(const __grid_con
                         tc_mma_mxf4(acc, wdesc + adv, xdesc + adv, idesc, sft + C::kColSfw + 4 * g, sfb, (ks > w.ks0 || kb > 0) ? 1u : 0u);
                         if (p.exact) tc_mma_mxf4(acc, cdesc + adv, xdesc + adv, idesc, sft + C::kColSfw2 + 4 * g, sfb, 1u);
                     }
-                    tc_commit(empty_bar(s));      // frees the stage once these MMAs have read it
+                    tc_commit(empty_bar(s));                      // frees the stage once these MMAs have read it
+                    if (p.exact) tc_commit(corr_empty_bar(cb));   // and the correction tile
                 }
                 tc_commit(acc_full_bar(buf));     // accumulator of this unit complete (or abandoned)
             }
@@ -334,10 +341,12 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_mxf4_kernel(const __grid_con
                 for (int ks = w.ks0; ks < w.ks1; ++ks, ++it) {
                     const int s = it % C::kStages;
                     const uint32_t ph = (it / C::kStages) & 1;
-                    ok = __all_sync(0xFFFFFFFFu, mbar_wait(full_bar(s), ph, abort_flag));   // warp-uniform decision
+                    const int cb = it % C::kCorrBufs;
+                    const uint32_t cph = (it / C::kCorrBufs) & 1;
+                    ok = __all_sync(0xFFFFFFFFu, mbar_wait(corr_empty_bar(cb), cph ^ 1u, abort_flag) && mbar_wait(full_bar(s), ph, abort_flag));
                     if (!ok) break;
                     const uint4* src = reinterpret_cast<const uint4*>(base_ptr + s * C::kStageBytes);
-                    uint4* dst = reinterpret_cast<uint4*>(base_ptr + s * C::kStageBytes + C::kOffC);
+                    uint4* dst = reinterpret_cast<uint4*>(corr_ptr + cb * C::kWBytes);
                     // all loads first, then the bit work, then all stores: eight independent chains per thread
                     uint4 v[C::kWBytes / 16 / 128];
 #pragma unroll
