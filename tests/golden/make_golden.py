@@ -94,7 +94,7 @@ def adversarial_blocks_bf16():
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="path to a checkout of moizyousufi/MoizMXFP4-public")
     ap.add_argument("--skip-fullsize", action="store_true")
     args = ap.parse_args()
     sys.path.insert(0, os.path.join(args.reference, "src"))
