@@ -183,7 +183,7 @@ struct GemmParams {
     int* status;
 };
 
-constexpr int kThreads = 352;   // warps: 0 producer, 1 MMA, 2-5 transform, 6-9 epilogue, 10 scale-factor copier
+constexpr int kThreads = 480;   // warps: 0 producer, 1 MMA, 2-5 and 11-14 transform, 6-9 epilogue, 10 scale-factor copier
 
 // A work unit is (k-range, weight tile, activation tile); units are dealt round-robin to the CTAs of
 // a persistent grid.  All roles walk the same unit sequence.
@@ -234,7 +234,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_mxf4_kernel(const __grid_con
         for (int s = 0; s < C::kStages; ++s) {
             mbar_init(full_bar(s), 1);
             mbar_init(empty_bar(s), 1);
-            mbar_init(ready_bar(s), p.exact ? 5 : 1);
+            mbar_init(ready_bar(s), p.exact ? 9 : 1);        // 8 transform warps + the copier's commit
             mbar_init(sfld_bar(s), 1);
         }
         for (int c = 0; c < C::kCorrBufs; ++c) mbar_init(corr_empty_bar(c), 1);
@@ -330,10 +330,10 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_mxf4_kernel(const __grid_con
             }
         }
         __syncwarp();
-    } else if (warp < 6) {
-        // ------------------------------------------------------------------ correction transform (EXACT mode)
+    } else if (warp < 6 || warp > 10) {
+        // ------------------------------------------------------------------ correction transform (EXACT mode), 8 warps
         if (p.exact) {
-            const int t = threadIdx.x - 64;       // 0..127
+            const int t = (warp < 6 ? warp - 2 : warp - 7) * 32 + lane;       // 0..255
             uint32_t it = 0;
             bool ok = true;
             for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x) {
@@ -348,15 +348,15 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_mxf4_kernel(const __grid_con
                     const uint4* src = reinterpret_cast<const uint4*>(base_ptr + s * C::kStageBytes);
                     uint4* dst = reinterpret_cast<uint4*>(corr_ptr + cb * C::kWBytes);
                     // all loads first, then the bit work, then all stores: eight independent chains per thread
-                    uint4 v[C::kWBytes / 16 / 128];
+                    uint4 v[C::kWBytes / 16 / 256];
 #pragma unroll
-                    for (int j = 0; j < C::kWBytes / 16 / 128; ++j) v[j] = src[j * 128 + t];
+                    for (int j = 0; j < C::kWBytes / 16 / 256; ++j) v[j] = src[j * 256 + t];
 #pragma unroll
-                    for (int j = 0; j < C::kWBytes / 16 / 128; ++j) {
+                    for (int j = 0; j < C::kWBytes / 16 / 256; ++j) {
                         v[j].x = corr_word(v[j].x); v[j].y = corr_word(v[j].y); v[j].z = corr_word(v[j].z); v[j].w = corr_word(v[j].w);
                     }
 #pragma unroll
-                    for (int j = 0; j < C::kWBytes / 16 / 128; ++j) dst[j * 128 + t] = v[j];   // same offset in and out: the swizzle is preserved
+                    for (int j = 0; j < C::kWBytes / 16 / 256; ++j) dst[j * 256 + t] = v[j];   // same offset in and out: the swizzle is preserved
                     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // make the writes visible to the tensor core
                     __syncwarp();
                     if (lane == 0) mbar_arrive(ready_bar(s));
@@ -416,61 +416,6 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_mxf4_kernel(const __grid_con
             const int n = n0 + lane;
             const float bias = (!split && p.bias != nullptr && n < p.N) ? __bfloat162float(p.bias[n]) : 0.0f;
             const bool has_bias = !split && p.bias != nullptr;
-            if constexpr (C::kAccBufs == 1) {
-                // Single accumulator: drain the whole tile row into registers as bf16 pairs first and hand the
-                // accumulator back at once, so that the next unit's MMAs run while this one is being stored.
-                uint32_t pk[BN / 2];
-#pragma unroll
-                for (int c0 = 0; c0 < BN; c0 += 32) {
-                    if (w.m_tile * BN + c0 < p.M) {               // uniform across the warp
-                        uint32_t v[32];
-                        tc_ld_32x32(tmem + ((uint32_t)(q * 32) << 16) + c0, v);
-#pragma unroll
-                        for (int j = 0; j < 32; j += 2) {
-                            __nv_bfloat16 y0 = __float2bfloat16_rn(__uint_as_float(v[j])), y1 = __float2bfloat16_rn(__uint_as_float(v[j + 1]));
-                            if (has_bias) {                        // `output += bias` in bf16
-                                y0 = __float2bfloat16_rn(__bfloat162float(y0) + bias);
-                                y1 = __float2bfloat16_rn(__bfloat162float(y1) + bias);
-                            }
-                            pk[(c0 + j) / 2] = (uint32_t)__bfloat16_as_ushort(y0) | ((uint32_t)__bfloat16_as_ushort(y1) << 16);
-                        }
-                    }
-                }
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(acc_empty_bar(buf));
-                uint16_t* t16 = reinterpret_cast<uint16_t*>(tile);
-                const bool vec = (p.ldo % 8 == 0) && (((uintptr_t)p.out) % 16 == 0) && (n0 + 32 <= p.N);
-#pragma unroll
-                for (int c0 = 0; c0 < BN; c0 += 32) {
-                    const int m0 = w.m_tile * BN + c0;
-                    if (m0 < p.M) {
-#pragma unroll
-                        for (int j = 0; j < 32; j += 2) {
-                            t16[j * 32 + lane] = (uint16_t)(pk[(c0 + j) / 2] & 0xFFFFu);
-                            t16[(j + 1) * 32 + lane] = (uint16_t)(pk[(c0 + j) / 2] >> 16);
-                        }
-                        __syncwarp();
-#pragma unroll
-                        for (int r = 0; r < 4; ++r) {
-                            const int row = r * 8 + (lane >> 2), seg = lane & 3;
-                            const int m = m0 + row;
-                            if (m < p.M) {
-                                if (vec) {
-                                    *reinterpret_cast<uint4*>(p.out + (int64_t)m * p.ldo + n0 + seg * 8) =
-                                        *reinterpret_cast<const uint4*>(t16 + row * 32 + seg * 8);
-                                } else {
-                                    for (int e = 0; e < 8; ++e)
-                                        if (n0 + seg * 8 + e < p.N)
-                                            p.out[(int64_t)m * p.ldo + n0 + seg * 8 + e] = __ushort_as_bfloat16(t16[row * 32 + seg * 8 + e]);
-                                }
-                            }
-                        }
-                        __syncwarp();
-                    }
-                }
-                continue;
-            }
 #pragma unroll 1
             for (int c0 = 0; c0 < BN; c0 += 32) {
                 const int m0 = w.m_tile * BN + c0;
