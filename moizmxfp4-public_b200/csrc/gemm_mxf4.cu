@@ -183,7 +183,7 @@ struct GemmParams {
     int* status;
 };
 
-constexpr int kThreads = 480;   // warps: 0 producer, 1 MMA, 2-5 and 11-14 transform, 6-9 epilogue, 10 scale-factor copier
+constexpr int kThreads = 512;   // warps: 0 producer, 1 and 15 MMA issuers, 2-5 and 11-14 transform, 6-9 epilogue, 10 scale-factor copier
 
 // A work unit is (k-range, weight tile, activation tile); units are dealt round-robin to the CTAs of
 // a persistent grid.  All roles walk the same unit sequence.
@@ -223,7 +223,10 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_mxf4_kernel(const __grid_con
     auto corr_empty_bar = [&](int c) { return bars + 8u * (5 * C::kStages + c); };   // MMAs have finished with a correction tile
     auto acc_full_bar = [&](int b) { return bars + 8u * (5 * C::kStages + C::kCorrBufs + b); };
     auto acc_empty_bar = [&](int b) { return bars + 8u * (5 * C::kStages + C::kCorrBufs + 2 + b); };
-    uint8_t* tail = epi_ptr + C::kEpiBytes + 8 * (5 * C::kStages + C::kCorrBufs + 4);
+    // "the overwriting MMA of unit i has been issued", one barrier per unit parity (the issuers are never more than
+    // one unit apart, so a barrier is never two phases ahead of a waiter)
+    auto unit_started_bar = [&](int i) { return bars + 8u * (5 * C::kStages + C::kCorrBufs + 4 + (i & 1)); };
+    uint8_t* tail = epi_ptr + C::kEpiBytes + 8 * (5 * C::kStages + C::kCorrBufs + 6);
     volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(tail);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tail + 4);
 
@@ -239,9 +242,11 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_mxf4_kernel(const __grid_con
         }
         for (int c = 0; c < C::kCorrBufs; ++c) mbar_init(corr_empty_bar(c), 1);
         for (int b = 0; b < 2; ++b) {
-            mbar_init(acc_full_bar(b), 1);
+            mbar_init(acc_full_bar(b), 2);        // both MMA issuers commit
             mbar_init(acc_empty_bar(b), 4);
         }
+        mbar_init(unit_started_bar(0), 1);
+        mbar_init(unit_started_bar(1), 1);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -286,9 +291,15 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_mxf4_kernel(const __grid_con
             }
         }
         __syncwarp();
-    } else if (warp == 1) {
-        // ------------------------------------------------------------------ MMA issuer
+    } else if (warp == 1 || warp == 15) {
+        // ------------------------------------------------------------------ MMA issuers
+        // Issuing a tcgen05.mma blocks while earlier MMAs execute (the queue is shallow), so whatever one thread does
+        // between two stages -- barrier wait, fence, commits -- would leave the tensor pipe idle.  Two threads
+        // therefore take alternate stages: while one is blocked issuing, the other has already done its waiting.
+        // Only the MMA that overwrites the accumulator (first of a unit) has to be issued before the others of
+        // its unit; the thread that owns it signals `unit_started`, the other one waits for that once per unit.
         if (lane == 0) {
+            const uint32_t me = warp == 1 ? 0u : 1u;
             const uint32_t idesc0 = make_idesc(BN, 0), idesc2 = make_idesc(BN, 2);
             uint32_t it = 0;
             int i = 0;                // units done by this CTA
@@ -303,7 +314,14 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_mxf4_kernel(const __grid_con
                 ok = mbar_wait(acc_empty_bar(buf), acc_ph ^ 1u, abort_flag);   // epilogue has drained this buffer
                 if (!ok) break;
                 tc_fence_after();
+                bool order_ok = ((it & 1u) == me);          // this thread owns the unit's first stage: nothing to wait for
                 for (int ks = w.ks0; ks < w.ks1; ++ks, ++it) {
+                    if ((it & 1u) != me) continue;           // the other issuer's stage
+                    if (!order_ok) {
+                        ok = mbar_wait(unit_started_bar(i), ((uint32_t)i >> 1) & 1u, abort_flag);
+                        if (!ok) break;
+                        order_ok = true;
+                    }
                     const int s = it % C::kStages;
                     const uint32_t ph = (it / C::kStages) & 1;
                     ok = mbar_wait(ready_bar(s), ph, abort_flag);   // tiles landed, correction built, scales in tensor memory
@@ -321,6 +339,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_mxf4_kernel(const __grid_con
                         const uint64_t adv = (uint64_t)(kb * 32 >> 4);             // 64 elements = 32 bytes along K
                         const uint32_t sfb = sfx_col + 4 * C::kXT * g;
                         tc_mma_mxf4(acc, wdesc + adv, xdesc + adv, idesc, sft + C::kColSfw + 4 * g, sfb, (ks > w.ks0 || kb > 0) ? 1u : 0u);
+                        if (ks == w.ks0 && kb == 0) mbar_arrive(unit_started_bar(i));
                         if (p.exact) tc_mma_mxf4(acc, cdesc + adv, xdesc + adv, idesc, sft + C::kColSfw2 + 4 * g, sfb, 1u);
                     }
                     tc_commit(empty_bar(s));                      // frees the stage once these MMAs have read it
