@@ -183,7 +183,7 @@ struct GemmParams {
     int* status;
 };
 
-constexpr int kThreads = 512;   // warps: 0 producer, 1 and 15 MMA issuers, 2-5 and 11-14 transform, 6-9 epilogue, 10 scale-factor copier
+constexpr int kThreads = 544;   // warps: 0 producer, 1 and 15 MMA issuers, 2-5 and 11-14 transform, 6-9 epilogue, 10 and 16 scale-factor copiers
 
 // A work unit is (k-range, weight tile, activation tile); units are dealt round-robin to the CTAs of
 // a persistent grid.  All roles walk the same unit sequence.
@@ -237,7 +237,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_mxf4_kernel(const __grid_con
         for (int s = 0; s < C::kStages; ++s) {
             mbar_init(full_bar(s), 1);
             mbar_init(empty_bar(s), 1);
-            mbar_init(ready_bar(s), p.exact ? 9 : 1);        // 8 transform warps + the copier's commit
+            mbar_init(ready_bar(s), p.exact ? 10 : 2);       // 8 transform warps (EXACT) + the two copiers' commits
             mbar_init(sfld_bar(s), 1);
         }
         for (int c = 0; c < C::kCorrBufs; ++c) mbar_init(corr_empty_bar(c), 1);
@@ -349,7 +349,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_mxf4_kernel(const __grid_con
             }
         }
         __syncwarp();
-    } else if (warp < 6 || warp > 10) {
+    } else if (warp < 6 || (warp > 10 && warp < 15)) {
         // ------------------------------------------------------------------ correction transform (EXACT mode), 8 warps
         if (p.exact) {
             const int t = (warp < 6 ? warp - 2 : warp - 7) * 32 + lane;       // 0..255
@@ -382,7 +382,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_mxf4_kernel(const __grid_con
                 }
             }
         }
-    } else if (warp == 10) {
+    } else if (warp == 10 || warp == 16) {
         // ------------------------------------------------------------------ scale-factor copier
         // Shared memory -> tensor memory with tcgen05.cp, one column set per pipeline stage.  Issuing these
         // copies costs the issuing thread a few hundred cycles per stage, so they live here and not in the MMA
@@ -401,17 +401,24 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_mxf4_kernel(const __grid_con
                     tc_fence_after();
                     const uint32_t st = base + s * C::kStageBytes;
                     const uint32_t sft = tmem + s * C::kSfSetCols;
+                    if (warp == 10) {
+                        // weight scales (both passes); this copier also vouches for the operand tiles
 #pragma unroll
-                    for (int g = 0; g < 2; ++g) {
-                        tc_cp_sf(sft + C::kColSfw + 4 * g, desc_sf(st + C::kOffSfw + 512 * g));
-                        if (p.exact) tc_cp_sf(sft + C::kColSfw2 + 4 * g, desc_sf(st + C::kOffSfw + 1024 + 512 * g));
+                        for (int g = 0; g < 2; ++g) {
+                            tc_cp_sf(sft + C::kColSfw + 4 * g, desc_sf(st + C::kOffSfw + 512 * g));
+                            if (p.exact) tc_cp_sf(sft + C::kColSfw2 + 4 * g, desc_sf(st + C::kOffSfw + 1024 + 512 * g));
+                        }
+                        // the copies are under way; "ready" must also imply that the operand tiles have landed
+                        ok = mbar_wait(full_bar(s), ph, abort_flag);
+                        if (!ok) break;
+                    } else {
+                        // activation scales
 #pragma unroll
-                        for (int t = 0; t < C::kXT; ++t)
-                            tc_cp_sf(sft + C::kColSfx + 4 * C::kXT * g + 4 * t, desc_sf(st + C::kOffSfx + 1024 * t + 512 * g));
+                        for (int g = 0; g < 2; ++g)
+#pragma unroll
+                            for (int t = 0; t < C::kXT; ++t)
+                                tc_cp_sf(sft + C::kColSfx + 4 * C::kXT * g + 4 * t, desc_sf(st + C::kOffSfx + 1024 * t + 512 * g));
                     }
-                    // the copies are under way; "ready" must also imply that the operand tiles have landed
-                    ok = mbar_wait(full_bar(s), ph, abort_flag);
-                    if (!ok) break;
                     tc_commit(ready_bar(s));
                 }
             }
