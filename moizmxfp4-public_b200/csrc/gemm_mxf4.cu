@@ -540,6 +540,32 @@ __global__ void __launch_bounds__(256) splitk_reduce_kernel(const float* __restr
     }
 }
 
+// Same sum, four consecutive columns per thread (128-bit loads of the partials, one 64-bit store); needs N % 4 == 0,
+// ldo % 4 == 0 and an 8-byte-aligned output.
+__global__ void __launch_bounds__(256) splitk_reduce4_kernel(const float4* __restrict__ partial, int ksplit, int64_t M, int64_t N,
+                                                             const __nv_bfloat16* __restrict__ bias, __nv_bfloat16* __restrict__ out, int64_t ldo) {
+    const int64_t total4 = M * N / 4;
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total4; i += (int64_t)gridDim.x * blockDim.x) {
+        float4 acc = __ldcs(partial + i);
+        for (int s = 1; s < ksplit; ++s) {
+            const float4 v = __ldcs(partial + (int64_t)s * total4 + i);
+            acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+        }
+        const int64_t e = i * 4, m = e / N, n = e - m * N;
+        float r[4] = {acc.x, acc.y, acc.z, acc.w};
+        __nv_bfloat16 y[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            y[j] = __float2bfloat16_rn(r[j]);
+            if (bias) y[j] = __float2bfloat16_rn(__bfloat162float(y[j]) + __bfloat162float(bias[n + j]));
+        }
+        uint2 o;
+        o.x = (uint32_t)__bfloat16_as_ushort(y[0]) | ((uint32_t)__bfloat16_as_ushort(y[1]) << 16);
+        o.y = (uint32_t)__bfloat16_as_ushort(y[2]) | ((uint32_t)__bfloat16_as_ushort(y[3]) << 16);
+        *reinterpret_cast<uint2*>(out + m * ldo + n) = o;
+    }
+}
+
 // ---------------------------------------------------------------- host side
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -614,7 +640,8 @@ int pick_ksplit(int64_t M, int64_t N, int64_t K) {
     int64_t best_cost = (tiles + sms - 1) / sms * (nks + 2);
     for (int ks = 2; ks <= 32 && ks <= nks; ++ks) {
         const int64_t rounds = (tiles * ks + sms - 1) / sms;
-        const int64_t cost = rounds * ((nks + ks - 1) / ks + 2) + 3;
+        // + fixed cost of the reduction + its traffic (partials written and read: ks*M*N*8 bytes, ~5 MB per stage time)
+        const int64_t cost = rounds * ((nks + ks - 1) / ks + 2) + 3 + (int64_t)ks * M * N * 8 / 5000000;
         if (cost < best_cost) { best_cost = cost; best = ks; }
     }
     return best;
@@ -682,11 +709,13 @@ int gemm_run(const uint8_t* a_packed, const uint8_t* a_sf_blocked, const uint8_t
     }
     if (rc) return rc;
     if (p.ksplit > 1) {
-        const int64_t total = M * N;
+        const bool vec = N % 4 == 0 && ldo % 4 == 0 && (uintptr_t)p.out % 8 == 0;
+        const int64_t total = vec ? M * N / 4 : M * N;
         int64_t grid = (total + 255) / 256;
         const int64_t cap = (int64_t)num_sms() * 16;
         if (grid > cap) grid = cap;
-        splitk_reduce_kernel<<<(unsigned)grid, 256, 0, st>>>(p.partial, p.ksplit, M, N, p.bias, p.out, ldo);
+        if (vec) splitk_reduce4_kernel<<<(unsigned)grid, 256, 0, st>>>((const float4*)p.partial, p.ksplit, M, N, p.bias, p.out, ldo);
+        else splitk_reduce_kernel<<<(unsigned)grid, 256, 0, st>>>(p.partial, p.ksplit, M, N, p.bias, p.out, ldo);
         MXFP4_CHECK_LAUNCH("mxfp4_gemm (split-K reduction)");
     }
     return MXFP4_OK;
