@@ -166,6 +166,89 @@ def quant_matmul_2d(input: torch.Tensor, packed_weight: torch.Tensor, weight_sca
     return out if in_dtype == torch.bfloat16 else out.to(in_dtype)
 
 
+class _HostPipe:
+    """Per-device staging for quant_matmul_host: three streams (host->device, GEMM, device->host) and a ring of
+    device chunk buffers, each with the events that say when it may be overwritten."""
+
+    def __init__(self, dev, depth=3):
+        self.dev, self.depth = dev, depth
+        self.s_in, self.s_mm, self.s_out = (torch.cuda.Stream(dev) for _ in range(3))
+        self.slots = []            # dicts: x, y, ev_in, ev_mm, ev_out, used
+        self.shape = None
+
+    def ring(self, rows, K, N):
+        if self.shape != (rows, K, N):
+            for s in (self.s_in, self.s_mm, self.s_out):
+                s.synchronize()
+            self.slots = [dict(x=torch.empty(rows, K, dtype=torch.bfloat16, device=self.dev),
+                               y=torch.empty(rows, N, dtype=torch.bfloat16, device=self.dev),
+                               ev_in=torch.cuda.Event(), ev_mm=torch.cuda.Event(), ev_out=torch.cuda.Event(), used=False)
+                          for _ in range(self.depth)]
+            self.shape = (rows, K, N)
+        return self.slots
+
+
+_host_pipes = {}                 # device index -> _HostPipe
+
+
+def quant_matmul_host(input: torch.Tensor, packed_weight: torch.Tensor, weight_scales: torch.Tensor,
+                      bias: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
+                      chunk_rows: int = 1024) -> torch.Tensor:
+    """quant_matmul for activations that live in HOST memory: [M,K] (pinned for full overlap) x device-resident packed
+    weight -> [M,N] bf16 in host memory (`out`, pinned; allocated when None).
+
+    The rows are cut into chunks; the host->device copy of chunk i+1, the GEMM of chunk i and the device->host copy of
+    chunk i-1 run on three streams, so the PCIe link is busy in both directions while the tensor cores work.  Rows are
+    independent and no chunk is small enough to be K-split unless M itself is, so the result equals quant_matmul's on
+    the same rows bit for bit.  The call returns after enqueueing; the current stream waits for the last device->host
+    copy, so synchronise it (or the device) before reading `out` on the host."""
+    assert input.dim() == 2 and packed_weight.dim() == 2
+    if input.is_cuda:
+        raise ValueError("quant_matmul_host takes host activations; use quant_matmul for device tensors")
+    _capi.require_cuda(packed_weight, "quant_matmul_host")
+    dev = packed_weight.device
+    M, K = input.shape
+    N = packed_weight.shape[0]
+    in_dtype = input.dtype
+    x = input if in_dtype == torch.bfloat16 else input.to(torch.bfloat16)
+    if out is None:
+        out = torch.empty(M, N, dtype=torch.bfloat16).pin_memory()
+    if out.dtype != torch.bfloat16 or out.shape != (M, N) or out.is_cuda:
+        raise ValueError("quant_matmul_host: out must be a host bf16 tensor of shape [M, N]")
+    if M == 0 or N == 0:
+        return out if in_dtype == torch.bfloat16 else out.to(in_dtype)
+    n_chunks = -(-M // max(int(chunk_rows), 129))
+    rows = _align(-(-M // n_chunks), 128)
+    with _lock:
+        pipe = _host_pipes.get(dev.index)
+        if pipe is None:
+            pipe = _host_pipes[dev.index] = _HostPipe(dev)
+        slots = pipe.ring(rows, K, N)
+        cur = torch.cuda.current_stream(dev)
+        pipe.s_mm.wait_stream(cur)                       # the weight (and bias) may have been produced on the caller's stream
+        for c, r0 in enumerate(range(0, M, rows)):
+            n = min(rows, M - r0)
+            sl = slots[c % pipe.depth]
+            if sl["used"]:
+                pipe.s_in.wait_event(sl["ev_mm"])        # the GEMM that read this x buffer has finished
+            with torch.cuda.stream(pipe.s_in):
+                sl["x"][:n].copy_(x[r0:r0 + n], non_blocking=True)
+                sl["ev_in"].record(pipe.s_in)
+            pipe.s_mm.wait_event(sl["ev_in"])
+            if sl["used"]:
+                pipe.s_mm.wait_event(sl["ev_out"])       # the copy that read this y buffer has finished
+            with torch.cuda.stream(pipe.s_mm):
+                quant_matmul_2d(sl["x"][:n], packed_weight, weight_scales, bias, out=sl["y"][:n])
+                sl["ev_mm"].record(pipe.s_mm)
+            pipe.s_out.wait_event(sl["ev_mm"])
+            with torch.cuda.stream(pipe.s_out):
+                out[r0:r0 + n].copy_(sl["y"][:n], non_blocking=True)
+                sl["ev_out"].record(pipe.s_out)
+            sl["used"] = True
+        cur.wait_stream(pipe.s_out)
+    return out if in_dtype == torch.bfloat16 else out.to(in_dtype)
+
+
 def _matmul_bf16_scales(input, packed_weight, weight_scales, bias):
     """scale_format="bf16" weights have no power-of-two scales, so they cannot feed the block-scaled
     tensor-core path; they take the reference's own formulation (dequantise, cast, dense matmul,

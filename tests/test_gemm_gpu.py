@@ -220,3 +220,24 @@ def test_block_stack_fused_projections_bit_identical():
         a, b = fused(x), plain(x)
     gemm.check_status()
     assert torch.isfinite(a.float()).all() and torch.equal(a, b)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("M,chunk", [(2500, 1024), (1025, 1024), (100, 1024), (3000, 512)])
+def test_quant_matmul_host_equals_device_path(M, chunk):
+    """Host-buffer pipeline (chunked copy in / GEMM / copy out on three streams) returns exactly what quant_matmul returns
+    for the same rows on the device, on two calls in a row (the second reuses the staging ring)."""
+    import mxfp4
+    N, K = 1536, 2048
+    dev = torch.device("cuda", 0)
+    packed, scales = mxfp4.MXFP4Quantizer(32, "e8m0").quantize(weight(N, K, 5, False).to(dev))
+    bias = (torch.randn(N, generator=torch.Generator().manual_seed(9)) * 0.1).to(torch.bfloat16).to(dev)
+    for rep in range(2):
+        x = act(M, K, 40 + rep)
+        want = mxfp4.quant_matmul(x.to(dev), packed, scales, bias).cpu()
+        got = mxfp4.quant_matmul_host(x.pin_memory(), packed, scales, bias, chunk_rows=chunk)
+        torch.cuda.synchronize()
+        assert got.dtype == torch.bfloat16 and not got.is_cuda
+        assert torch.equal(got.view(torch.int16), want.view(torch.int16))
+    with pytest.raises(ValueError):
+        mxfp4.quant_matmul_host(x.to(dev), packed, scales)
