@@ -129,7 +129,8 @@ class MXBlockStack(nn.Module):
 
     @staticmethod
     def _norm(h):
-        return (h.float() * torch.rsqrt(h.float().pow(2).mean(-1, keepdim=True) + 1e-6)).to(h.dtype)
+        # one fused kernel; the composed form (float, pow, mean, rsqrt, mul, cast) was six launches and a fifth of a decode step
+        return torch.nn.functional.rms_norm(h, (h.shape[-1],), eps=1e-6)
 
     @classmethod
     def build(cls, n_layers=32, hidden=4096, inter=11008, device="cuda", group=None, seed=0, block_size=32, fuse=True):
