@@ -455,6 +455,22 @@ int make_map(CUtensorMap* map, const void* ptr, int64_t rows, int64_t row_bytes,
     return MXFP4_OK;
 }
 
+// bf16 matrix [rows, cols] with row pitch ld elements, boxes of 32 x 32, no swizzle (the epilogue's TMA stores).
+// Needs a 16-byte aligned base and a pitch that is a multiple of 16 bytes; returns MXFP4_E_ALIGN otherwise.
+int make_out_map(CUtensorMap* map, const void* ptr, int64_t rows, int64_t cols, int64_t ld) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) { set_error("cuTensorMapEncodeTiled is not available from this driver"); return MXFP4_E_CUDA; }
+    if ((uintptr_t)ptr % 16 || (ld * 2) % 16) return MXFP4_E_ALIGN;
+    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    cuuint32_t box[2] = {32, 32};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) { set_error("cuTensorMapEncodeTiled (output) failed with CUresult %d", (int)r); return MXFP4_E_CUDA; }
+    return MXFP4_OK;
+}
+
 template <int BN>
 int launch_gemm(const CUtensorMap& mw, const CUtensorMap& mx, GemmParams& p, cudaStream_t st) {
     using C = Cfg<BN>;
@@ -570,7 +586,15 @@ int gemm_run(const uint8_t* a_packed, const uint8_t* a_sf_blocked, const uint8_t
     }
     p.exact = mode == MXFP4_GEMM_EXACT; p.status = status_dev;
     cudaStream_t st = (cudaStream_t)stream;
-    if (pair_bn) return launch_gemm_pair(pair_bn, mw, mx, p, st);
+    p.tma_store = 0;
+    if (pair_bn) {
+        CUtensorMap mo;
+        const int orc = make_out_map(&mo, out_bf16, M, N, ldo);
+        if (orc == MXFP4_E_CUDA) return orc;
+        p.tma_store = orc == MXFP4_OK;          // an unaligned output keeps the plain stores
+        if (!p.tma_store) mo = mw;              // any valid map: the kernel does not touch it
+        return launch_gemm_pair(pair_bn, mw, mx, mo, p, st);
+    }
     switch (bn) {
         case 32: rc = launch_gemm<32>(mw, mx, p, st); break;
         case 64: rc = launch_gemm<64>(mw, mx, p, st); break;

@@ -27,14 +27,26 @@ __device__ __forceinline__ uint32_t map_to_cta(uint32_t saddr, uint32_t rank) {
     asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(saddr), "r"(rank));
     return r;
 }
+// Arrive on a barrier of the other CTA.  Default semantics (release at CTA scope), as is customary for signalling
+// inside a cluster: a release at cluster scope costs the arriving thread a fence of well over a thousand cycles, which
+// put every report of the peer CTA on the critical path.  What the reports order is already complete when they are
+// sent: tensor-memory stores after tcgen05.wait::st, shared-memory writes after fence.proxy.async.
 __device__ __forceinline__ void mbar_arrive_remote(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// per-stage report of the peer CTA to the leader's ready barrier
+__device__ __forceinline__ void mbar_report_remote(uint32_t cluster_addr) {
+#if defined(MXFP4_PAIR_DIAG_RELCLUSTER)
     asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+#elif !defined(MXFP4_PAIR_DIAG_NOPEER)
+    mbar_arrive_remote(cluster_addr);
+#endif
 }
 __device__ __forceinline__ bool mbar_try_wait_cl(uint32_t bar, uint32_t parity) {
     uint32_t ok;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}"
         : "=r"(ok)
         : "r"(bar), "r"(parity)
@@ -54,20 +66,39 @@ __device__ __forceinline__ bool mbar_wait_cl(uint32_t bar, uint32_t parity, vola
     *abort_flag = 1;
     return false;
 }
+// The same with a non-blocking test in a spin loop (the two MMA-issuing threads)
+__device__ __forceinline__ bool mbar_spin_cl(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+#ifdef MXFP4_PAIR_NOSPIN
+    return mbar_wait_cl(bar, parity, abort_flag);
+#else
+    const long long t0 = clock64();
+    for (uint32_t it = 1;; ++it) {
+        uint32_t ok;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok)
+            : "r"(bar), "r"(parity)
+            : "memory");
+        if (ok) return true;
+        if ((it & 255u) == 0) {
+            if (*abort_flag) return false;
+            if (clock64() - t0 > kWaitLimitCycles) break;
+        }
+    }
+    *abort_flag = 1;
+    return false;
+#endif
+}
 __device__ __forceinline__ void cluster_sync_all() {
     asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
 
-__device__ __forceinline__ void tc2_commit(uint32_t bar) {          // arrives on this CTA's barrier
-    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
 __device__ __forceinline__ void tc2_commit_both(uint32_t bar) {     // arrives on the same barrier of both CTAs
     asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(bar),
                  "h"((uint16_t)3)
                  : "memory");
-}
-__device__ __forceinline__ void tc2_cp_sf(uint32_t tmem_addr, uint64_t sdesc) {
-    asm volatile("tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], %1;" ::"r"(tmem_addr), "l"(sdesc) : "memory");
 }
 __device__ __forceinline__ void tc2_mma_mxf4(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t sfa, uint32_t sfb,
                                              uint32_t accumulate) {
@@ -78,9 +109,54 @@ __device__ __forceinline__ void tc2_mma_mxf4(uint32_t d_tmem, uint64_t adesc, ui
         "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(sfa), "r"(sfb)
         : "memory");
 }
+// TMA tile load whose completion bytes go to a barrier of either CTA of the pair (a shared::cluster address)
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, uint32_t bar_cluster, int x, int y) {
+    asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(dst),
+                 "l"(map), "r"(bar_cluster), "r"(x), "r"(y)
+                 : "memory");
+}
 // instruction descriptor as make_idesc, with M = 256 (128 rows in each CTA)
 __device__ __forceinline__ uint32_t make_idesc_pair(int n, uint32_t sf_id) {
     return (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | (1u << 23) | ((uint32_t)(256 >> 4) << 24) | (sf_id << 29) | (sf_id << 4);
+}
+
+// warps: 0 TMA producer, 1 and 15 MMA issuers (leader CTA), 2-5 scale-factor writers (one per tensor-memory lane
+// quarter), 6-9 and 19-22 epilogue (two warps per lane quarter, half of the columns each), 10-14 and 16-18
+// correction transform (EXACT mode)
+constexpr int kPairThreads = 736;
+
+// tcgen05.ld of a 32-lane x 32-column block without waiting for it; tc_wait_ld makes the values usable
+__device__ __forceinline__ void tc_ld_32x32_nowait(uint32_t taddr, uint32_t (&v)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,"
+        "%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]), "=r"(v[9]), "=r"(v[10]),
+          "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]),
+          "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]),
+          "=r"(v[31])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tc_wait_ld(uint32_t (&v)[32]) {
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+    // the values are defined only now: tie every register to a statement that follows the wait
+    asm volatile("" : "+r"(v[0]), "+r"(v[1]), "+r"(v[2]), "+r"(v[3]), "+r"(v[4]), "+r"(v[5]), "+r"(v[6]), "+r"(v[7]), "+r"(v[8]), "+r"(v[9]), "+r"(v[10]),
+                      "+r"(v[11]), "+r"(v[12]), "+r"(v[13]), "+r"(v[14]), "+r"(v[15]));
+    asm volatile("" : "+r"(v[16]), "+r"(v[17]), "+r"(v[18]), "+r"(v[19]), "+r"(v[20]), "+r"(v[21]), "+r"(v[22]), "+r"(v[23]), "+r"(v[24]), "+r"(v[25]),
+                      "+r"(v[26]), "+r"(v[27]), "+r"(v[28]), "+r"(v[29]), "+r"(v[30]), "+r"(v[31]));
+}
+
+// 32 lanes x 32 bits, N consecutive columns, registers -> tensor memory
+__device__ __forceinline__ void tc_st_x16(uint32_t taddr, const uint4& a, const uint4& b, const uint4& c, const uint4& d) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};" ::"r"(taddr), "r"(a.x),
+                 "r"(a.y), "r"(a.z), "r"(a.w), "r"(b.x), "r"(b.y), "r"(b.z), "r"(b.w), "r"(c.x), "r"(c.y), "r"(c.z), "r"(c.w), "r"(d.x), "r"(d.y),
+                 "r"(d.z), "r"(d.w)
+                 : "memory");
+}
+__device__ __forceinline__ void tc_st_x8(uint32_t taddr, const uint4& a, const uint4& b) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"r"(taddr), "r"(a.x), "r"(a.y), "r"(a.z), "r"(a.w),
+                 "r"(b.x), "r"(b.y), "r"(b.z), "r"(b.w)
+                 : "memory");
 }
 
 template <int BN>
@@ -89,31 +165,30 @@ struct PairCfg {
     static constexpr int kXT = BN <= 128 ? 1 : 2;                  // 128-row groups of activation scales a tile can touch
     static constexpr int kWBytes = kTileW * kStageKBytes;          // 16 KB
     static constexpr int kXBytes = kHalf * kStageKBytes;
-    static constexpr int kSfwBytes = 2048;
-    static constexpr int kSfxBytes = 1024 * kXT;                   // scales of the WHOLE activation tile, in both CTAs
     static constexpr int kOffX = kWBytes;
-    static constexpr int kOffSfw = kOffX + kXBytes;
-    static constexpr int kOffSfx = kOffSfw + kSfwBytes;
-    static constexpr int kStageBytes = (kOffSfx + kSfxBytes + 1023) / 1024 * 1024;
-    static constexpr int kCorrBufs = 2;
+    static constexpr int kStageBytes = kWBytes + kXBytes;          // a pipeline slot holds the two operand tiles only
+    static constexpr int kCorrBufs = 3;                            // ring of correction tiles (EXACT mode)
     static constexpr int kCorrBytes = kCorrBufs * kWBytes;
-    static constexpr int kEpiBytes = 4 * 4096;
+    static constexpr int kEpiBytes = 8 * 2048;                     // per epilogue warp: 32 x 32 bf16 for the transpose
     static constexpr int kAccBufs = BN <= 192 ? 2 : 1;
     static constexpr int kAccStride = BN <= 128 ? 128 : (BN <= 192 ? 192 : 256);
-    // tensor memory: the accumulators, then one set of scale-factor columns per MMA-issuing thread
+    // tensor memory: the accumulators, then a ring of scale-factor column sets
     static constexpr int kColSf = kAccBufs * kAccStride;
     static constexpr int kSfSetCols = 32;
     static constexpr int kColSfw = kColSf;         // 2 K-tiles x 4 columns (pass 1)
     static constexpr int kColSfw2 = kColSf + 8;    // same for pass 2
     static constexpr int kColSfx = kColSf + 16;    // 2 K-tiles x 4*kXT columns
-    static constexpr int kBudget = 227 * 1024 - 1024 - 512 - kEpiBytes - kCorrBytes;
+    static constexpr int kBudget = 227 * 1024 - 1024 - 1024 - kEpiBytes - kCorrBytes;
     static constexpr int kBySmem = kBudget / kStageBytes;
     static constexpr int kStages = kBySmem < 8 ? kBySmem : 8;
-    static constexpr int kSmemBytes = kStages * kStageBytes + kCorrBytes + kEpiBytes + 1024 + 512;
-    static constexpr uint32_t kTxBytes = kWBytes + kXBytes + kSfwBytes + kSfxBytes;   // everything a CTA loads for a stage
+    static constexpr int kByTmem = (512 - kColSf) / kSfSetCols;
+    static constexpr int kSfSets = kByTmem < 8 ? kByTmem : 8;      // a deeper ring than the operand pipeline: the peer's reports get a head start
+    static constexpr int kSmemBytes = kStages * kStageBytes + kCorrBytes + kEpiBytes + 1024 + 1024;
+    static constexpr uint32_t kTxBytes = kWBytes + kXBytes;
+    static constexpr int kSfRegs = 4 + 2 * kXT;    // 128-bit words of scale factors a thread moves per stage
     static constexpr int kTmemCols = 512;
     static_assert(BN % 32 == 0 && BN <= 256 && kHalf % 8 == 0, "tile width");
-    static_assert(kStages >= 2 && 16 + 8 * kXT <= kSfSetCols && kColSf + 2 * kSfSetCols <= 512, "pipeline depth / tensor memory");
+    static_assert(kStages >= 2 && kSfSets >= 2 && 16 + 8 * kXT <= kSfSetCols && kStageBytes % 1024 == 0, "pipeline depth / tensor memory");
 };
 
 // Work units of the pair kernel: (pair of weight tiles, activation tile); no K split (large M only).
@@ -128,8 +203,9 @@ __device__ __forceinline__ PairUnit get_pair_unit(const GemmParams& p, int n_pai
 }
 
 template <int BN>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
-    gemm_mxf4_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, const GemmParams p) {
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
+    gemm_mxf4_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+                          const __grid_constant__ CUtensorMap map_out, const GemmParams p) {
     using C = PairCfg<BN>;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
@@ -140,18 +216,25 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
     uint8_t* epi_ptr = corr_ptr + C::kCorrBytes;
     const uint32_t bars = corr_base + C::kCorrBytes + C::kEpiBytes;
     // in every CTA, signalled locally or by the leader's multicast commits
-    auto full_bar = [&](int s) { return bars + 8u * s; };                        // this CTA's operand and scale tiles have landed
+    auto full_bar = [&](int s) { return bars + 8u * s; };                        // EXACT mode: this CTA's weight tile has landed (the transform waits for it)
     auto empty_bar = [&](int s) { return bars + 8u * (C::kStages + s); };        // MMAs have finished with the stage (both CTAs)
     // used in the leader only; the peer's arrivals come in remotely
-    auto ready_bar = [&](int s) { return bars + 8u * (3 * C::kStages + s); };    // both CTAs: tiles landed, correction built
+    auto ready_bar = [&](int s) { return bars + 8u * (3 * C::kStages + s); };    // EXACT mode: both CTAs have built their correction tiles
+    auto tiles_bar = [&](int s) { return bars + 8u * (2 * C::kStages + s); };    // TMA bytes of BOTH CTAs: activation halves, in FAST mode also the weight tiles
+    auto sfe_bar = [&](int k) { return bars + 8u * (5 * C::kStages + C::kCorrBufs + 6 + k); };   // in every CTA: MMAs have finished with scale column set k
     auto corr_empty_bar = [&](int c) { return bars + 8u * (5 * C::kStages + c); };
     auto acc_full_bar = [&](int b) { return bars + 8u * (5 * C::kStages + C::kCorrBufs + b); };
     auto acc_empty_bar = [&](int b) { return bars + 8u * (5 * C::kStages + C::kCorrBufs + 2 + b); };   // leader: 8 epilogue warps of the pair
     auto unit_started_bar = [&](int i) { return bars + 8u * (5 * C::kStages + C::kCorrBufs + 4 + (i & 1)); };
-    uint8_t* tail = epi_ptr + C::kEpiBytes + 8 * (5 * C::kStages + C::kCorrBufs + 6);
+    auto sfr_bar = [&](int k) { return bars + 8u * (5 * C::kStages + C::kCorrBufs + 6 + C::kSfSets + k); };   // leader: both CTAs have written set k
+    uint8_t* tail = epi_ptr + C::kEpiBytes + 8 * (5 * C::kStages + C::kCorrBufs + 6 + 2 * C::kSfSets);
+    static_assert(8 * (5 * C::kStages + C::kCorrBufs + 6 + 2 * C::kSfSets) + 8 <= 1024, "barrier area");
     volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(tail);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tail + 4);
 
+#ifdef MXFP4_PAIR_PROF
+    __shared__ volatile long long prof_ts[8][4];
+#endif
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = cluster_ctarank();          // 0 = leader
     const bool leader = rank == 0;
@@ -163,13 +246,17 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
         for (int s = 0; s < C::kStages; ++s) {
             mbar_init(full_bar(s), 1);
             mbar_init(empty_bar(s), 1);
-            // one "tiles landed" report per CTA; in EXACT mode also the 8 + 8 transform warps
-            mbar_init(ready_bar(s), p.exact ? 18 : 2);
+            mbar_init(tiles_bar(s), 1);
+            mbar_init(ready_bar(s), 16);          // 8 + 8 transform warps
         }
         for (int c = 0; c < C::kCorrBufs; ++c) mbar_init(corr_empty_bar(c), 1);
+        for (int k = 0; k < C::kSfSets; ++k) {
+            mbar_init(sfe_bar(k), 1);
+            mbar_init(sfr_bar(k), 8);             // 4 + 4 scale-factor warps
+        }
         for (int b = 0; b < 2; ++b) {
             mbar_init(acc_full_bar(b), 2);        // both MMA issuers commit (multicast to both CTAs)
-            mbar_init(acc_empty_bar(b), 8);       // 4 epilogue warps in each CTA
+            mbar_init(acc_empty_bar(b), 16);      // 8 epilogue warps in each CTA
         }
         mbar_init(unit_started_bar(0), 1);
         mbar_init(unit_started_bar(1), 1);
@@ -188,17 +275,24 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
     cluster_sync_all();                               // the peer's barriers exist before anything arrives on them
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
+#ifdef MXFP4_PAIR_DIAG_STAGGER
+    {   // timing experiment: pairs start a few hundred cycles apart
+        const long long t0 = clock64();
+        const long long d = (long long)(blockIdx.x >> 1) * MXFP4_PAIR_DIAG_STAGGER;
+        while (clock64() - t0 < d) {}
+    }
+#endif
 
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer (each CTA loads its own tiles)
         if (lane == 0) {
             uint32_t it = 0;
             bool ok = true;
+            const uint32_t tiles0 = map_to_cta(tiles_bar(0), 0);
             for (int u = first_unit; u < total_units && ok; u += unit_step) {
                 const PairUnit w = get_pair_unit(p, n_pairs, u);
                 const int m0 = w.m_tile * BN;
                 const int n_tile = w.n_pair * 2 + (int)rank;
-                const int sf_tile = n_tile < p.n_tiles ? n_tile : p.n_tiles - 1;     // a tile past the end reads a valid one; nothing of it is stored
                 for (int ks = 0; ks < p.kstages; ++ks, ++it) {
                     const int s = it % C::kStages;
                     const uint32_t ph = (it / C::kStages) & 1;
@@ -207,19 +301,22 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 #endif
                     if (!mbar_wait_cl(empty_bar(s), ph ^ 1u, abort_flag)) { ok = false; break; }
 #ifdef MXFP4_PAIR_PROF
-                    reinterpret_cast<long long*>(p.status)[1024 + blockIdx.x * 8 + 4] += clock64() - pt0;
+                    (void)pt0;
+                    prof_ts[s][1] = clock64();
 #endif
                     const uint32_t st = base + s * C::kStageBytes;
-                    mbar_expect_tx(full_bar(s), C::kTxBytes);
-                    tma_load_2d(st, &map_w, full_bar(s), ks * kStageKBytes, n_tile * kTileW);
-                    tma_load_2d(st + C::kOffX, &map_x, full_bar(s), ks * kStageKBytes, m0 + (int)rank * C::kHalf);
-                    bulk_load(st + C::kOffSfw, p.sfw + ((int64_t)sf_tile * p.kstages + ks) * 2048, 2048, full_bar(s));
-#pragma unroll
-                    for (int t = 0; t < C::kXT; ++t) {
-                        int64_t grp = m0 / 128 + t;
-                        if (grp * 128 >= ((int64_t)p.M + 127) / 128 * 128) grp = m0 / 128;
-                        bulk_load(st + C::kOffSfx + t * 1024, p.sfx + (grp * p.kstages + ks) * 1024, 1024, full_bar(s));
+                    // The leader's barrier counts the bytes of both CTAs (its own expect_tx may come after the peer's
+                    // bytes: the count goes negative for a moment, the phase cannot complete before the arrive).
+                    const uint32_t tb = tiles0 + 8u * s;
+                    if (p.exact) {
+                        if (leader) mbar_expect_tx(tiles_bar(s), 2 * C::kXBytes);
+                        mbar_expect_tx(full_bar(s), C::kWBytes);
+                        tma_load_2d(st, &map_w, full_bar(s), ks * kStageKBytes, n_tile * kTileW);
+                    } else {
+                        if (leader) mbar_expect_tx(tiles_bar(s), 2 * C::kTxBytes);
+                        tma_load_2d_pair(st, &map_w, tb, ks * kStageKBytes, n_tile * kTileW);
                     }
+                    tma_load_2d_pair(st + C::kOffX, &map_x, tb, ks * kStageKBytes, m0 + (int)rank * C::kHalf);
                 }
             }
         }
@@ -248,7 +345,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
                 const uint32_t acc = tmem + buf * C::kAccStride;
                 const uint32_t sfx_off = ((w.m_tile * BN) % 128) / 32;
                 PROF_T(ta0);
-                ok = mbar_wait_cl(acc_empty_bar(buf), acc_ph ^ 1u, abort_flag);   // both CTAs' epilogues have drained this buffer
+                ok = mbar_spin_cl(acc_empty_bar(buf), acc_ph ^ 1u, abort_flag);   // both CTAs' epilogues have drained this buffer
                 if (!ok) break;
                 PROF_T(ta1);
                 PROF_ADD(3, ta1 - ta0);
@@ -257,35 +354,36 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
                 for (int ks = 0; ks < p.kstages; ++ks, ++it) {
                     if ((it & 1u) != me) continue;
                     if (!order_ok) {
+                        PROF_T(tu0);
                         ok = mbar_wait(unit_started_bar(i), ((uint32_t)i >> 1) & 1u, abort_flag);
                         if (!ok) break;
                         order_ok = true;
+                        PROF_T(tu1);
+                        PROF_ADD(4, tu1 - tu0);
                     }
                     const int s = it % C::kStages;
                     const uint32_t ph = (it / C::kStages) & 1;
                     PROF_T(tr0);
-#ifdef MXFP4_PAIR_PROF
-                    if (!mbar_try_wait_cl(ready_bar(s), ph)) pf[2] += 1;
-#endif
-                    ok = mbar_wait_cl(ready_bar(s), ph, abort_flag);
+                    ok = mbar_spin_cl(tiles_bar(s), ph, abort_flag);
+                    PROF_T(tw1);
+                    ok = ok && mbar_spin_cl(sfr_bar(it % C::kSfSets), (it / C::kSfSets) & 1, abort_flag);
+                    PROF_T(tw2);
+                    ok = ok && (!p.exact || mbar_spin_cl(ready_bar(s), ph, abort_flag));
                     if (!ok) break;
                     tc_fence_after();
                     PROF_T(tr1);
-                    PROF_ADD(1, tr1 - tr0);
+                    PROF_ADD(1, tw2 - tr0);      // tiles + scales
+                    PROF_ADD(2, tr1 - tw2);      // correction tiles
                     PROF_ADD(7, 1);
-                    const uint32_t st = base + s * C::kStageBytes;
-                    // Scale factors, shared -> tensor memory in both SMs, into this thread's own column set.  Copies
-                    // and MMAs of one thread execute in issue order, so the MMAs below see them and the copies of
-                    // this thread's next stage cannot overtake these MMAs.
-                    const uint32_t sft = tmem + me * C::kSfSetCols;
-#pragma unroll
-                    for (int g = 0; g < 2; ++g) {
-                        tc2_cp_sf(sft + C::kColSfw + 4 * g, desc_sf(st + C::kOffSfw + 512 * g));
-                        if (p.exact) tc2_cp_sf(sft + C::kColSfw2 + 4 * g, desc_sf(st + C::kOffSfw + 1024 + 512 * g));
-#pragma unroll
-                        for (int t = 0; t < C::kXT; ++t)
-                            tc2_cp_sf(sft + C::kColSfx + 4 * C::kXT * g + 4 * t, desc_sf(st + C::kOffSfx + 1024 * t + 512 * g));
+#ifdef MXFP4_PAIR_PROF
+                    if (it >= (uint32_t)C::kStages) {
+                        long long* hp = reinterpret_cast<long long*>(p.status) + 1024 + (blockIdx.x + 1) * 8;
+                        const long long A = prof_ts[s][0], B = prof_ts[s][1], Cc = prof_ts[s][2];
+                        hp[0] += B - A; hp[3] += 1; hp[5] += tr1 - A; (void)Cc;
                     }
+#endif
+                    const uint32_t st = base + s * C::kStageBytes;
+                    const uint32_t sft = tmem + (it % C::kSfSets) * C::kSfSetCols;       // this stage's scale-factor columns
                     const uint32_t sfx_col = sft + C::kColSfx + sfx_off;
                     const int cb = it % C::kCorrBufs;
                     const uint64_t wdesc = desc_sw128(st), cdesc = desc_sw128(corr_base + cb * C::kWBytes), xdesc = desc_sw128(st + C::kOffX);
@@ -302,9 +400,13 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
                     PROF_T(ti1);
                     PROF_ADD(5, ti1 - tr1);
                     tc2_commit_both(empty_bar(s));
+                    tc2_commit_both(sfe_bar(it % C::kSfSets));
                     if (p.exact) tc2_commit_both(corr_empty_bar(cb));
                     PROF_T(tc1);
                     PROF_ADD(6, tc1 - ti1);
+#ifdef MXFP4_PAIR_PROF
+                    prof_ts[s][0] = tc1;
+#endif
                 }
                 tc2_commit_both(acc_full_bar(buf));
             }
@@ -312,16 +414,15 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
             if (me == 0) {
                 pf[0] = clock64() - pstart;
                 long long* dstp = reinterpret_cast<long long*>(p.status) + 1024 + blockIdx.x * 8;
-                for (int j = 0; j < 8; ++j)
-                    if (j != 4) dstp[j] = pf[j];
+                for (int j = 0; j < 8; ++j) dstp[j] = pf[j];
             }
 #endif
         }
         __syncwarp();
-    } else if (warp < 6 || (warp > 10 && warp < 15)) {
+    } else if (warp >= 10 && warp < 19) {
         // ------------------------------------------------------------------ correction transform (EXACT mode), 8 warps per CTA
         if (p.exact) {
-            const int t = (warp < 6 ? warp - 2 : warp - 7) * 32 + lane;
+            const int t = (warp < 15 ? warp - 10 : warp - 11) * 32 + lane;       // warps 10-14 -> 0-4, 16-18 -> 5-7
             uint32_t it = 0;
             bool ok = true;
             for (int u = first_unit; u < total_units && ok; u += unit_step) {
@@ -332,6 +433,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
                     const uint32_t cph = (it / C::kCorrBufs) & 1;
                     ok = __all_sync(0xFFFFFFFFu, mbar_wait_cl(corr_empty_bar(cb), cph ^ 1u, abort_flag) && mbar_wait(full_bar(s), ph, abort_flag));
                     if (!ok) break;
+#ifdef MXFP4_PAIR_PROF
+                    if (warp == 10 && lane == 0) prof_ts[s][2] = clock64();
+#endif
                     const uint4* src = reinterpret_cast<const uint4*>(base_ptr + s * C::kStageBytes);
                     uint4* dst = reinterpret_cast<uint4*>(corr_ptr + cb * C::kWBytes);
                     uint4 v[C::kWBytes / 16 / 256];
@@ -347,34 +451,83 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
                     __syncwarp();
                     if (lane == 0) {
                         if (leader) mbar_arrive(ready_bar(s));
-                        else mbar_arrive_remote(map_to_cta(ready_bar(s), 0));
+                        else mbar_report_remote(map_to_cta(ready_bar(s), 0));
                     }
                 }
             }
         }
-    } else if (warp == 10 || warp == 16) {
-        // ------------------------------------------------------------------ "tiles landed" report to the leader's ready barrier
-        if (warp == 10 && lane == 0) {
+    } else if (warp < 6) {
+        // ------------------------------------------------------------------ scale factors: global -> registers -> tensor memory
+        // tcgen05.cp would put these copies into the same in-order pipe as the MMAs, where each one costs more than
+        // a hundred cycles.  Four warps (one per lane quarter: the layout wants the 32 rows of a scale tile
+        // replicated in all four) load the prepared tiles straight from global memory, one stage ahead, and write
+        // them with tcgen05.st, beside the MMAs and independent of the operand pipeline.  Thread l owns row l of
+        // every 32 x 16-byte scale tile: one 128-bit load per tile, four columns of its lane.
+        {
+            const uint32_t lane_base = ((uint32_t)(warp & 3) * 32u) << 16;
+            const uint32_t sfr0 = leader ? 0u : map_to_cta(sfr_bar(0), 0);
+            const int64_t m_groups_end = ((int64_t)p.M + 127) / 128 * 128;
+            auto load_sf = [&](int u, int ks, uint4 (&r)[C::kSfRegs]) {
+                const PairUnit w = get_pair_unit(p, n_pairs, u);
+                const int n_tile = w.n_pair * 2 + (int)rank;
+                const int sf_tile = n_tile < p.n_tiles ? n_tile : p.n_tiles - 1;     // a tile past the end reads a valid one; nothing of it is stored
+                const uint8_t* wp = p.sfw + ((int64_t)sf_tile * p.kstages + ks) * 2048 + lane * 16;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) r[j] = __ldg(reinterpret_cast<const uint4*>(wp + 512 * j));      // pass 1: K halves 0, 1; pass 2: K halves 0, 1
+                const int m0 = w.m_tile * BN;
+#pragma unroll
+                for (int t = 0; t < C::kXT; ++t) {
+                    int64_t grp = m0 / 128 + t;
+                    if (grp * 128 >= m_groups_end) grp = m0 / 128;      // a group past the end: its rows are beyond M and never stored
+                    const uint8_t* xp = p.sfx + (grp * p.kstages + ks) * 1024 + lane * 16;
+#pragma unroll
+                    for (int g = 0; g < 2; ++g) r[4 + C::kXT * g + t] = __ldg(reinterpret_cast<const uint4*>(xp + 512 * g));   // column order: K half, then group
+                }
+            };
+            uint4 cur[C::kSfRegs], nxt[C::kSfRegs];
+            if (first_unit < total_units) load_sf(first_unit, 0, cur);
             uint32_t it = 0;
             bool ok = true;
-            const uint32_t ready0 = leader ? 0u : map_to_cta(ready_bar(0), 0);
             for (int u = first_unit; u < total_units && ok; u += unit_step) {
                 for (int ks = 0; ks < p.kstages; ++ks, ++it) {
-                    const int s = it % C::kStages;
-                    const uint32_t ph = (it / C::kStages) & 1;
-                    ok = mbar_wait(full_bar(s), ph, abort_flag);
+                    // the MMAs that read this column set (kSfSets stages ago) must have completed
+                    ok = __all_sync(0xFFFFFFFFu, mbar_wait_cl(sfe_bar(it % C::kSfSets), ((it / C::kSfSets) & 1) ^ 1u, abort_flag));
                     if (!ok) break;
-                    if (leader) mbar_arrive(ready_bar(s));
-                    else mbar_arrive_remote(ready0 + 8u * s);
+                    tc_fence_after();
+                    const uint32_t sft = tmem + lane_base + (it % C::kSfSets) * C::kSfSetCols;
+                    tc_st_x16(sft + C::kColSfw, cur[0], cur[1], cur[2], cur[3]);
+                    if constexpr (C::kXT == 2) tc_st_x16(sft + C::kColSfx, cur[4], cur[5], cur[6], cur[7]);
+                    else tc_st_x8(sft + C::kColSfx, cur[4], cur[5]);
+                    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) {
+                        const int k = it % C::kSfSets;
+                        if (leader) mbar_arrive(sfr_bar(k));
+                        else mbar_report_remote(sfr0 + 8u * k);
+                    }
+                    // Fetch the next stage's scales only now: a release-arrive waits for the thread's outstanding
+                    // loads, so a prefetch issued before it would delay the report by a trip to L2.  The loads
+                    // complete while this warp waits for the next column set to become free.
+                    int nu = u, nks = ks + 1;
+                    if (nks == p.kstages) { nks = 0; nu = u + unit_step; }
+                    if (nu < total_units) load_sf(nu, nks, nxt);
+#pragma unroll
+                    for (int j = 0; j < C::kSfRegs; ++j) cur[j] = nxt[j];
                 }
             }
         }
-        __syncwarp();
     } else {
         // ------------------------------------------------------------------ epilogue (each CTA stores its own 128 weight rows)
+        // Eight warps: lane quarter q = warp % 4 (the quarter a warp may read), column half h.  The tensor-memory load
+        // of the next 32-column block is in flight while the current one is converted, transposed through shared memory
+        // (so that 32 consecutive n of a row go out as 16-byte stores) and stored.
+        const int e = warp < 10 ? warp - 6 : warp - 15;       // 0..7
         const int q = warp & 3;
-        uint32_t* tile = reinterpret_cast<uint32_t*>(epi_ptr + (warp - 6) * 4096);
+        const int h = warp < 10 ? 0 : 1;
+        __nv_bfloat16* t16 = reinterpret_cast<__nv_bfloat16*>(epi_ptr + e * 2048);
         const bool has_bias = p.bias != nullptr;
+        const bool vec_ok = (p.ldo % 8 == 0) && (((uintptr_t)p.out) % 16 == 0);
         int i = 0;
         bool ok = true;
         for (int u = first_unit; u < total_units && ok; u += unit_step, ++i) {
@@ -384,51 +537,125 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
             ok = __all_sync(0xFFFFFFFFu, ok && !*abort_flag);
             if (!ok) break;
             tc_fence_after();
+#ifdef MXFP4_PAIR_PROF
+            const long long ep0 = clock64();
+            long long ep1 = 0;
+#endif
             const int n0 = (w.n_pair * 2 + (int)rank) * kTileW + q * 32;
             const int n = n0 + lane;
             const float bias = (has_bias && n < p.N) ? __bfloat162float(p.bias[n]) : 0.0f;
-            bool released = false;
-#pragma unroll 1
-            for (int c0 = 0; c0 < BN; c0 += 32) {
-                const int m0 = w.m_tile * BN + c0;
-                if (m0 >= p.M) break;
-                uint32_t v[32];
-                tc_ld_32x32(tmem + buf * C::kAccStride + ((uint32_t)(q * 32) << 16) + c0, v);
-                if (c0 + 32 >= BN || m0 + 32 >= p.M) {
-                    tc_fence_before();
-                    __syncwarp();
-                    if (lane == 0) {
-                        if (leader) mbar_arrive(acc_empty_bar(buf));
-                        else mbar_arrive_remote(map_to_cta(acc_empty_bar(buf), 0));
-                    }
-                    released = true;
+            const bool vec = vec_ok && (n0 + 32 <= p.N);
+            const int mbeg = w.m_tile * BN + h * (BN / 2);                  // first activation row of this warp's columns
+            const int rows_left = p.M - mbeg;
+            const int nchunk = rows_left <= 0 ? 0 : (rows_left >= BN / 2 ? BN / 64 : (rows_left + 31) / 32);
+            const uint32_t taddr0 = tmem + buf * C::kAccStride + ((uint32_t)(q * 32) << 16) + h * (BN / 2);
+            auto release = [&]() {                                           // every load of this warp has completed
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) {
+                    if (leader) mbar_arrive(acc_empty_bar(buf));
+                    else mbar_arrive_remote(map_to_cta(acc_empty_bar(buf), 0));
                 }
-                __nv_bfloat16* t16 = reinterpret_cast<__nv_bfloat16*>(tile);
+#ifdef MXFP4_PAIR_PROF
+                ep1 = clock64();
+#endif
+            };
+#ifdef MXFP4_PAIR_PROF
+            long long sb[3] = {0, 0, 0};
+#endif
+            auto store_block = [&](const uint32_t (&v)[32], int c) {
+                const int m0 = mbeg + c * 32;
+                if (p.tma_store) {
+                    // the previous tile must have been read out of shared memory before it is overwritten
+                    if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+                    __syncwarp();
+                }
+#ifdef MXFP4_PAIR_PROF
+                const long long s0 = clock64();
+#endif
 #pragma unroll
                 for (int j = 0; j < 32; ++j) {
                     __nv_bfloat16 y = __float2bfloat16_rn(__uint_as_float(v[j]));
-                    if (has_bias) y = __float2bfloat16_rn(__bfloat162float(y) + bias);
+                    if (has_bias) y = __float2bfloat16_rn(__bfloat162float(y) + bias);   // `output += bias` in bf16
                     t16[j * 32 + lane] = y;
                 }
+#ifdef MXFP4_PAIR_PROF
+                const long long s1 = clock64();
+#endif
+                if (p.tma_store) {
+                    // the 32 (m) x 32 (n) bf16 tile leaves as one TMA store; rows and columns past M, N are clipped
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    __syncwarp();
+                    if (lane == 0 && n0 < p.N) {
+                        asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(&map_out), "r"(smem_u32(t16)),
+                                     "r"(n0), "r"(m0)
+                                     : "memory");
+                        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                    }
+                    return;
+                }
                 __syncwarp();
-                const bool vec = (p.ldo % 8 == 0) && (((uintptr_t)p.out) % 16 == 0) && (n0 + 32 <= p.N);
+#ifdef MXFP4_PAIR_PROF
+                const long long s2 = clock64();
+#endif
 #pragma unroll
                 for (int r = 0; r < 4; ++r) {
                     const int row = r * 8 + (lane >> 2), seg = lane & 3;
                     const int m = m0 + row;
+#ifdef MXFP4_PAIR_DIAG_NOSTORE
+                    if (m < 0) {
+#else
                     if (m < p.M) {
+#endif
                         if (vec) {
                             *reinterpret_cast<uint4*>(p.out + (int64_t)m * p.ldo + n0 + seg * 8) = *reinterpret_cast<const uint4*>(t16 + row * 32 + seg * 8);
                         } else {
-                            for (int e = 0; e < 8; ++e)
-                                if (n0 + seg * 8 + e < p.N) p.out[(int64_t)m * p.ldo + n0 + seg * 8 + e] = t16[row * 32 + seg * 8 + e];
+                            for (int x = 0; x < 8; ++x)
+                                if (n0 + seg * 8 + x < p.N) p.out[(int64_t)m * p.ldo + n0 + seg * 8 + x] = t16[row * 32 + seg * 8 + x];
                         }
                     }
                 }
                 __syncwarp();
+#ifdef MXFP4_PAIR_PROF
+                sb[0] += s1 - s0; sb[1] += s2 - s1; sb[2] += clock64() - s2;
+#endif
+            };
+            uint32_t va[32], vb[32];
+            if (nchunk == 0) {
+                release();
+                continue;
             }
-            (void)released;
+            // Two blocks are loaded up front and each buffer is refilled as soon as its block has been written out, so the
+            // last tensor-memory load -- and with it the release of the accumulator -- comes two block stores before the end.
+            tc_ld_32x32_nowait(taddr0, va);
+            if (nchunk > 1) tc_ld_32x32_nowait(taddr0 + 32, vb);
+            tc_wait_ld(va);
+            if (nchunk > 1) tc_wait_ld(vb);
+            if (nchunk <= 2) release();
+#pragma unroll 1
+            for (int c = 0; c < nchunk; c += 2) {
+                store_block(va, c);
+                if (c + 2 < nchunk) tc_ld_32x32_nowait(taddr0 + (c + 2) * 32, va);
+                if (c + 1 < nchunk) store_block(vb, c + 1);
+                if (c + 3 < nchunk) tc_ld_32x32_nowait(taddr0 + (c + 3) * 32, vb);
+                if (c + 2 < nchunk) {
+                    tc_wait_ld(va);
+                    if (c + 3 < nchunk) tc_wait_ld(vb);
+                    if (c + 4 >= nchunk) release();        // those were the last loads
+                }
+            }
+            (void)0;
+#ifdef MXFP4_PAIR_PROF
+            if (leader && warp == 6 && lane == 0) {
+                long long* hp = reinterpret_cast<long long*>(p.status) + 1024 + (blockIdx.x + 1) * 8;
+                hp[4] += ep1 - ep0;
+                hp[7] += clock64() - ep1;
+                hp[1] += sb[0]; hp[2] += sb[1]; hp[6] += sb[2];
+            }
+#endif
         }
+        if (p.tma_store && lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");     // all tile stores of this warp are complete
+        __syncwarp();
     }
 
     // ---------------------------------------------------------------------- teardown
@@ -449,7 +676,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 }
 
 template <int BN>
-int launch_pair(const CUtensorMap& mw, const CUtensorMap& mx, GemmParams& p, cudaStream_t st) {
+int launch_pair(const CUtensorMap& mw, const CUtensorMap& mx, const CUtensorMap& mo, GemmParams& p, cudaStream_t st) {
     using C = PairCfg<BN>;
     static int clusters[64] = {0};       // co-resident CTA pairs per device, 0 = not configured yet
     int dev = 0;
@@ -460,7 +687,7 @@ int launch_pair(const CUtensorMap& mw, const CUtensorMap& mx, GemmParams& p, cud
         if (e != cudaSuccess) return cuda_fail(e, "mxfp4_gemm: cudaFuncSetAttribute (pair kernel)");
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3(2 * num_sms(), 1, 1);
-        cfg.blockDim = dim3(kThreads, 1, 1);
+        cfg.blockDim = dim3(kPairThreads, 1, 1);
         cfg.dynamicSmemBytes = C::kSmemBytes;
         cudaLaunchAttribute attr;
         attr.id = cudaLaunchAttributeClusterDimension;
@@ -475,18 +702,18 @@ int launch_pair(const CUtensorMap& mw, const CUtensorMap& mx, GemmParams& p, cud
     p.m_tiles = (p.M + BN - 1) / BN;
     const int64_t units = (int64_t)((p.n_tiles + 1) / 2) * p.m_tiles;
     const int pairs = (int)(units < clusters[dev] ? units : clusters[dev]);
-    gemm_mxf4_pair_kernel<BN><<<2 * pairs, kThreads, C::kSmemBytes, st>>>(mw, mx, p);
+    gemm_mxf4_pair_kernel<BN><<<2 * pairs, kPairThreads, C::kSmemBytes, st>>>(mw, mx, mo, p);
     MXFP4_CHECK_LAUNCH("mxfp4_gemm (tcgen05 cta_group::2 kernel)");
     return MXFP4_OK;
 }
 
 }  // namespace
 
-int launch_gemm_pair(int bn, const CUtensorMap& mw, const CUtensorMap& mx, GemmParams& p, cudaStream_t st) {
+int launch_gemm_pair(int bn, const CUtensorMap& mw, const CUtensorMap& mx, const CUtensorMap& mo, GemmParams& p, cudaStream_t st) {
     switch (bn) {
-        case 128: return launch_pair<128>(mw, mx, p, st);
-        case 192: return launch_pair<192>(mw, mx, p, st);
-        case 256: return launch_pair<256>(mw, mx, p, st);
+        case 128: return launch_pair<128>(mw, mx, mo, p, st);
+        case 192: return launch_pair<192>(mw, mx, mo, p, st);
+        case 256: return launch_pair<256>(mw, mx, mo, p, st);
     }
     set_error("mxfp4_gemm: no cta_group::2 kernel for tile width %d", bn);
     return MXFP4_E_BADARG;

@@ -20,10 +20,12 @@ struct GemmParams {
     int n_tiles, m_tiles;
     int exact;
     int* status;
+    int tma_store;          // cta_group::2 kernel: the output goes out as TMA tile stores (map_out is valid)
 };
 
 // cta_group::2 kernel (gemm_mxf4_pair.cu): tile widths 128, 192, 256; the activation map's box holds bn/2 rows
-int launch_gemm_pair(int bn, const CUtensorMap& map_w, const CUtensorMap& map_x, GemmParams& p, cudaStream_t stream);
+// map_out: bf16 [M, ldo] with 32 x 32 boxes; used when p.tma_store is set
+int launch_gemm_pair(int bn, const CUtensorMap& map_w, const CUtensorMap& map_x, const CUtensorMap& map_out, GemmParams& p, cudaStream_t stream);
 
 namespace {
 
