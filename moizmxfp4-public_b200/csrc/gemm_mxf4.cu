@@ -503,14 +503,20 @@ int pick_bn(int64_t M) {
     return pad256 * 100 <= M * 104 ? 256 : 128;
 }
 
-// Tile width of the cta_group::2 kernel, or 0 for the one-CTA kernel.  Pairs pay off when there is enough work to
-// fill the chip with 256-row weight tiles.  MXFP4_GEMM_PAIR=0/1 switches the path, MXFP4_GEMM_PAIR_BN picks the width.
-int pick_pair_bn(int64_t M, int64_t N) {
-    static const int enabled = [] { const char* e = getenv("MXFP4_GEMM_PAIR"); return e ? atoi(e) : 0; }();
-    static const int forced_bn = [] { const char* e = getenv("MXFP4_GEMM_PAIR_BN"); return e ? atoi(e) : 0; }();
-    if (!enabled || M < 512 || N < 256) return 0;
-    if (forced_bn == 128 || forced_bn == 192 || forced_bn == 256) return forced_bn;
-    return 192;
+// Tile width of the cta_group::2 kernel (gemm_mxf4_pair.cu), or 0 for the one-CTA kernel.  Measured on B200 against the
+// one-CTA kernel: in EXACT mode the pair kernel is 5-20 % faster from M = 512 up except for the smallest problems
+// (M <= 1024 with N <= 4096); in FAST mode it wins only up to M = 2048.  MXFP4_GEMM_PAIR=0 forces the one-CTA kernel,
+// MXFP4_GEMM_PAIR=1 the pair kernel wherever it can run; MXFP4_GEMM_PAIR_BN picks the width (128, 192, 256).
+int pick_pair_bn(int64_t M, int64_t N, bool exact) {
+    const char* e = getenv("MXFP4_GEMM_PAIR");
+    const int forced = e ? atoi(e) : -1;
+    if (forced == 0 || M < 512 || N < 256) return 0;
+    if (forced < 0) {
+        if (exact ? (M <= 1024 && N <= 4096) : (M > 2048)) return 0;
+    }
+    const char* b = getenv("MXFP4_GEMM_PAIR_BN");
+    const int bn = b ? atoi(b) : 0;
+    return (bn == 128 || bn == 192 || bn == 256) ? bn : 256;
 }
 
 // Number of K ranges.  Skinny problems have fewer tiles than SMs; cutting K spreads the weight stream over
@@ -567,7 +573,7 @@ int gemm_run(const uint8_t* a_packed, const uint8_t* a_sf_blocked, const uint8_t
         return MXFP4_E_ALIGN;
     }
     CUtensorMap mw, mx;
-    const int pair_bn = pick_pair_bn(M, N);            // 0: one-CTA kernel
+    const int pair_bn = pick_pair_bn(M, N, mode == MXFP4_GEMM_EXACT);            // 0: one-CTA kernel
     const int bn = pair_bn ? pair_bn : pick_bn(M);
     int rc = make_map(&mw, w_packed, N, K / 2, kTileW);
     if (rc) return rc;

@@ -6,10 +6,23 @@
 // each SM therefore reads half as many activation bytes from its shared memory as the one-CTA kernel does, which
 // is what bounds that kernel in EXACT mode.
 //
-// CTA 0 of the pair (the leader) issues every tcgen05.mma / tcgen05.cp / tcgen05.commit; the instructions execute
-// in both SMs, each on its own shared and tensor memory at the same addresses, so both CTAs keep identical
-// layouts.  Completion is multicast to the same barrier in both CTAs.  What the peer CTA produces (tiles landed,
-// correction tile built, accumulator drained) reaches the leader as remote mbarrier arrivals.
+// CTA 0 of the pair (the leader) issues every tcgen05.mma and tcgen05.commit; the instructions execute in both SMs,
+// each on its own shared and tensor memory at the same addresses, so both CTAs keep identical layouts.  Completion
+// (stage free, correction tile free, scale columns free, accumulator full) is multicast to the same barrier in both CTAs.
+//
+// What differs from the one-CTA kernel, each point measured:
+//  * Scale factors do not pass through shared memory or tcgen05.cp.  A tcgen05.cp sits in the same in-order pipe as
+//    the MMAs and cost over a hundred cycles each here; four warps per CTA (one per tensor-memory lane quarter) load
+//    the prepared scale tiles from global memory one stage ahead and write them with tcgen05.st into a ring of column
+//    sets that is deeper than the operand pipeline.
+//  * The operand tiles of BOTH CTAs complete their bytes on the leader's barrier (TMA with .cta_group::2), so the MMA
+//    thread learns of the peer's tiles without any thread of the peer in between.
+//  * What threads of the peer do produce per stage (scales written, correction tile built) and per tile (accumulator
+//    drained) reaches the leader as remote mbarrier arrives with CTA-scope release.  With cluster-scope release each
+//    arrive cost the sender a fence of more than a thousand cycles and the kernel ran 40 % slower.
+//  * One 256-column accumulator fills half of tensor memory and the scale ring the other half, so the epilogue cannot
+//    overlap the next tile.  Eight warps therefore drain the accumulator into registers (as bf16 pairs) first, hand it
+//    back, and only then transpose through shared memory and store, as TMA tile stores when the output is aligned.
 // Every wait is bounded as in the one-CTA kernel; both CTAs meet at a cluster barrier before they exit, so no
 // remote arrival can target a CTA that has gone.
 #include "gemm_mxf4_tc.cuh"
@@ -36,11 +49,7 @@ __device__ __forceinline__ void mbar_arrive_remote(uint32_t cluster_addr) {
 }
 // per-stage report of the peer CTA to the leader's ready barrier
 __device__ __forceinline__ void mbar_report_remote(uint32_t cluster_addr) {
-#if defined(MXFP4_PAIR_DIAG_RELCLUSTER)
-    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
-#elif !defined(MXFP4_PAIR_DIAG_NOPEER)
     mbar_arrive_remote(cluster_addr);
-#endif
 }
 __device__ __forceinline__ bool mbar_try_wait_cl(uint32_t bar, uint32_t parity) {
     uint32_t ok;
@@ -65,31 +74,6 @@ __device__ __forceinline__ bool mbar_wait_cl(uint32_t bar, uint32_t parity, vola
     }
     *abort_flag = 1;
     return false;
-}
-// The same with a non-blocking test in a spin loop (the two MMA-issuing threads)
-__device__ __forceinline__ bool mbar_spin_cl(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
-#ifdef MXFP4_PAIR_NOSPIN
-    return mbar_wait_cl(bar, parity, abort_flag);
-#else
-    const long long t0 = clock64();
-    for (uint32_t it = 1;; ++it) {
-        uint32_t ok;
-        asm volatile(
-            "{\n\t.reg .pred p;\n\t"
-            "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-            "selp.u32 %0, 1, 0, p;\n\t}"
-            : "=r"(ok)
-            : "r"(bar), "r"(parity)
-            : "memory");
-        if (ok) return true;
-        if ((it & 255u) == 0) {
-            if (*abort_flag) return false;
-            if (clock64() - t0 > kWaitLimitCycles) break;
-        }
-    }
-    *abort_flag = 1;
-    return false;
-#endif
 }
 __device__ __forceinline__ void cluster_sync_all() {
     asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
@@ -125,27 +109,6 @@ __device__ __forceinline__ uint32_t make_idesc_pair(int n, uint32_t sf_id) {
 // correction transform (EXACT mode)
 constexpr int kPairThreads = 736;
 
-// tcgen05.ld of a 32-lane x 32-column block without waiting for it; tc_wait_ld makes the values usable
-__device__ __forceinline__ void tc_ld_32x32_nowait(uint32_t taddr, uint32_t (&v)[32]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,"
-        "%26,%27,%28,%29,%30,%31}, [%32];"
-        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]), "=r"(v[9]), "=r"(v[10]),
-          "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]),
-          "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]),
-          "=r"(v[31])
-        : "r"(taddr)
-        : "memory");
-}
-__device__ __forceinline__ void tc_wait_ld(uint32_t (&v)[32]) {
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-    // the values are defined only now: tie every register to a statement that follows the wait
-    asm volatile("" : "+r"(v[0]), "+r"(v[1]), "+r"(v[2]), "+r"(v[3]), "+r"(v[4]), "+r"(v[5]), "+r"(v[6]), "+r"(v[7]), "+r"(v[8]), "+r"(v[9]), "+r"(v[10]),
-                      "+r"(v[11]), "+r"(v[12]), "+r"(v[13]), "+r"(v[14]), "+r"(v[15]));
-    asm volatile("" : "+r"(v[16]), "+r"(v[17]), "+r"(v[18]), "+r"(v[19]), "+r"(v[20]), "+r"(v[21]), "+r"(v[22]), "+r"(v[23]), "+r"(v[24]), "+r"(v[25]),
-                      "+r"(v[26]), "+r"(v[27]), "+r"(v[28]), "+r"(v[29]), "+r"(v[30]), "+r"(v[31]));
-}
-
 // 32 lanes x 32 bits, N consecutive columns, registers -> tensor memory
 __device__ __forceinline__ void tc_st_x16(uint32_t taddr, const uint4& a, const uint4& b, const uint4& c, const uint4& d) {
     asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};" ::"r"(taddr), "r"(a.x),
@@ -157,6 +120,18 @@ __device__ __forceinline__ void tc_st_x8(uint32_t taddr, const uint4& a, const u
     asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"r"(taddr), "r"(a.x), "r"(a.y), "r"(a.z), "r"(a.w),
                  "r"(b.x), "r"(b.y), "r"(b.z), "r"(b.w)
                  : "memory");
+}
+
+// 32 lanes x 16 columns, loaded and waited for
+__device__ __forceinline__ void tc_ld_32x16(uint32_t taddr, uint32_t (&v)[16]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+                 : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]), "=r"(v[9]), "=r"(v[10]),
+                   "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+                 : "r"(taddr)
+                 : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+    asm volatile("" : "+r"(v[0]), "+r"(v[1]), "+r"(v[2]), "+r"(v[3]), "+r"(v[4]), "+r"(v[5]), "+r"(v[6]), "+r"(v[7]), "+r"(v[8]), "+r"(v[9]), "+r"(v[10]),
+                      "+r"(v[11]), "+r"(v[12]), "+r"(v[13]), "+r"(v[14]), "+r"(v[15]));
 }
 
 template <int BN>
@@ -232,9 +207,6 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
     volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(tail);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tail + 4);
 
-#ifdef MXFP4_PAIR_PROF
-    __shared__ volatile long long prof_ts[8][4];
-#endif
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = cluster_ctarank();          // 0 = leader
     const bool leader = rank == 0;
@@ -275,13 +247,6 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
     cluster_sync_all();                               // the peer's barriers exist before anything arrives on them
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
-#ifdef MXFP4_PAIR_DIAG_STAGGER
-    {   // timing experiment: pairs start a few hundred cycles apart
-        const long long t0 = clock64();
-        const long long d = (long long)(blockIdx.x >> 1) * MXFP4_PAIR_DIAG_STAGGER;
-        while (clock64() - t0 < d) {}
-    }
-#endif
 
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer (each CTA loads its own tiles)
@@ -296,14 +261,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
                 for (int ks = 0; ks < p.kstages; ++ks, ++it) {
                     const int s = it % C::kStages;
                     const uint32_t ph = (it / C::kStages) & 1;
-#ifdef MXFP4_PAIR_PROF
-                    const long long pt0 = clock64();
-#endif
                     if (!mbar_wait_cl(empty_bar(s), ph ^ 1u, abort_flag)) { ok = false; break; }
-#ifdef MXFP4_PAIR_PROF
-                    (void)pt0;
-                    prof_ts[s][1] = clock64();
-#endif
                     const uint32_t st = base + s * C::kStageBytes;
                     // The leader's barrier counts the bytes of both CTAs (its own expect_tx may come after the peer's
                     // bytes: the count goes negative for a moment, the phase cannot complete before the arrive).
@@ -329,59 +287,30 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
             uint32_t it = 0;
             int i = 0;
             bool ok = true;
-#ifdef MXFP4_PAIR_PROF
-            long long pf[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-            const long long pstart = clock64();
-#define PROF_T(var) const long long var = clock64()
-#define PROF_ADD(i, v) pf[i] += (v)
-#else
-#define PROF_T(var)
-#define PROF_ADD(i, v)
-#endif
             for (int u = first_unit; u < total_units && ok; u += unit_step, ++i) {
                 const PairUnit w = get_pair_unit(p, n_pairs, u);
                 const int buf = i % C::kAccBufs;
                 const uint32_t acc_ph = (i / C::kAccBufs) & 1;
                 const uint32_t acc = tmem + buf * C::kAccStride;
                 const uint32_t sfx_off = ((w.m_tile * BN) % 128) / 32;
-                PROF_T(ta0);
-                ok = mbar_spin_cl(acc_empty_bar(buf), acc_ph ^ 1u, abort_flag);   // both CTAs' epilogues have drained this buffer
+                ok = mbar_wait_cl(acc_empty_bar(buf), acc_ph ^ 1u, abort_flag);   // both CTAs' epilogues have drained this buffer
                 if (!ok) break;
-                PROF_T(ta1);
-                PROF_ADD(3, ta1 - ta0);
                 tc_fence_after();
                 bool order_ok = ((it & 1u) == me);
                 for (int ks = 0; ks < p.kstages; ++ks, ++it) {
                     if ((it & 1u) != me) continue;
                     if (!order_ok) {
-                        PROF_T(tu0);
                         ok = mbar_wait(unit_started_bar(i), ((uint32_t)i >> 1) & 1u, abort_flag);
                         if (!ok) break;
                         order_ok = true;
-                        PROF_T(tu1);
-                        PROF_ADD(4, tu1 - tu0);
                     }
                     const int s = it % C::kStages;
                     const uint32_t ph = (it / C::kStages) & 1;
-                    PROF_T(tr0);
-                    ok = mbar_spin_cl(tiles_bar(s), ph, abort_flag);
-                    PROF_T(tw1);
-                    ok = ok && mbar_spin_cl(sfr_bar(it % C::kSfSets), (it / C::kSfSets) & 1, abort_flag);
-                    PROF_T(tw2);
-                    ok = ok && (!p.exact || mbar_spin_cl(ready_bar(s), ph, abort_flag));
+                    ok = mbar_wait_cl(tiles_bar(s), ph, abort_flag);
+                    ok = ok && mbar_wait_cl(sfr_bar(it % C::kSfSets), (it / C::kSfSets) & 1, abort_flag);
+                    ok = ok && (!p.exact || mbar_wait_cl(ready_bar(s), ph, abort_flag));
                     if (!ok) break;
                     tc_fence_after();
-                    PROF_T(tr1);
-                    PROF_ADD(1, tw2 - tr0);      // tiles + scales
-                    PROF_ADD(2, tr1 - tw2);      // correction tiles
-                    PROF_ADD(7, 1);
-#ifdef MXFP4_PAIR_PROF
-                    if (it >= (uint32_t)C::kStages) {
-                        long long* hp = reinterpret_cast<long long*>(p.status) + 1024 + (blockIdx.x + 1) * 8;
-                        const long long A = prof_ts[s][0], B = prof_ts[s][1], Cc = prof_ts[s][2];
-                        hp[0] += B - A; hp[3] += 1; hp[5] += tr1 - A; (void)Cc;
-                    }
-#endif
                     const uint32_t st = base + s * C::kStageBytes;
                     const uint32_t sft = tmem + (it % C::kSfSets) * C::kSfSetCols;       // this stage's scale-factor columns
                     const uint32_t sfx_col = sft + C::kColSfx + sfx_off;
@@ -397,26 +326,12 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
                         if (ks == 0 && kb == 0) mbar_arrive(unit_started_bar(i));
                         if (p.exact) tc2_mma_mxf4(acc, cdesc + adv, xdesc + adv, idesc, sft + C::kColSfw2 + 4 * g, sfb, 1u);
                     }
-                    PROF_T(ti1);
-                    PROF_ADD(5, ti1 - tr1);
                     tc2_commit_both(empty_bar(s));
                     tc2_commit_both(sfe_bar(it % C::kSfSets));
                     if (p.exact) tc2_commit_both(corr_empty_bar(cb));
-                    PROF_T(tc1);
-                    PROF_ADD(6, tc1 - ti1);
-#ifdef MXFP4_PAIR_PROF
-                    prof_ts[s][0] = tc1;
-#endif
                 }
                 tc2_commit_both(acc_full_bar(buf));
             }
-#ifdef MXFP4_PAIR_PROF
-            if (me == 0) {
-                pf[0] = clock64() - pstart;
-                long long* dstp = reinterpret_cast<long long*>(p.status) + 1024 + blockIdx.x * 8;
-                for (int j = 0; j < 8; ++j) dstp[j] = pf[j];
-            }
-#endif
         }
         __syncwarp();
     } else if (warp >= 10 && warp < 19) {
@@ -433,9 +348,6 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
                     const uint32_t cph = (it / C::kCorrBufs) & 1;
                     ok = __all_sync(0xFFFFFFFFu, mbar_wait_cl(corr_empty_bar(cb), cph ^ 1u, abort_flag) && mbar_wait(full_bar(s), ph, abort_flag));
                     if (!ok) break;
-#ifdef MXFP4_PAIR_PROF
-                    if (warp == 10 && lane == 0) prof_ts[s][2] = clock64();
-#endif
                     const uint4* src = reinterpret_cast<const uint4*>(base_ptr + s * C::kStageBytes);
                     uint4* dst = reinterpret_cast<uint4*>(corr_ptr + cb * C::kWBytes);
                     uint4 v[C::kWBytes / 16 / 256];
@@ -537,10 +449,6 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
             ok = __all_sync(0xFFFFFFFFu, ok && !*abort_flag);
             if (!ok) break;
             tc_fence_after();
-#ifdef MXFP4_PAIR_PROF
-            const long long ep0 = clock64();
-            long long ep1 = 0;
-#endif
             const int n0 = (w.n_pair * 2 + (int)rank) * kTileW + q * 32;
             const int n = n0 + lane;
             const float bias = (has_bias && n < p.N) ? __bfloat162float(p.bias[n]) : 0.0f;
@@ -556,103 +464,78 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
                     if (leader) mbar_arrive(acc_empty_bar(buf));
                     else mbar_arrive_remote(map_to_cta(acc_empty_bar(buf), 0));
                 }
-#ifdef MXFP4_PAIR_PROF
-                ep1 = clock64();
-#endif
             };
-#ifdef MXFP4_PAIR_PROF
-            long long sb[3] = {0, 0, 0};
-#endif
-            auto store_block = [&](const uint32_t (&v)[32], int c) {
-                const int m0 = mbeg + c * 32;
-                if (p.tma_store) {
-                    // the previous tile must have been read out of shared memory before it is overwritten
-                    if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
-                    __syncwarp();
-                }
-#ifdef MXFP4_PAIR_PROF
-                const long long s0 = clock64();
-#endif
+            // Phase 1: the warp's BN/2 columns leave tensor memory 16 at a time and stay in registers as bf16 pairs
+            // (m, m+1); the accumulator is handed back as soon as the last load has completed.
+            constexpr int kBlocks = BN / 64;                       // 32-column blocks per warp
+            uint32_t pk[kBlocks * 16];
 #pragma unroll
-                for (int j = 0; j < 32; ++j) {
-                    __nv_bfloat16 y = __float2bfloat16_rn(__uint_as_float(v[j]));
-                    if (has_bias) y = __float2bfloat16_rn(__bfloat162float(y) + bias);   // `output += bias` in bf16
-                    t16[j * 32 + lane] = y;
-                }
-#ifdef MXFP4_PAIR_PROF
-                const long long s1 = clock64();
-#endif
-                if (p.tma_store) {
-                    // the 32 (m) x 32 (n) bf16 tile leaves as one TMA store; rows and columns past M, N are clipped
-                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                    __syncwarp();
-                    if (lane == 0 && n0 < p.N) {
-                        asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(&map_out), "r"(smem_u32(t16)),
-                                     "r"(n0), "r"(m0)
-                                     : "memory");
-                        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-                    }
-                    return;
-                }
-                __syncwarp();
-#ifdef MXFP4_PAIR_PROF
-                const long long s2 = clock64();
-#endif
+            for (int c = 0; c < kBlocks * 2; ++c) {
+                if (c * 16 < nchunk * 32) {                        // warp-uniform
+                    uint32_t v[16];
+                    tc_ld_32x16(taddr0 + c * 16, v);
 #pragma unroll
-                for (int r = 0; r < 4; ++r) {
-                    const int row = r * 8 + (lane >> 2), seg = lane & 3;
-                    const int m = m0 + row;
-#ifdef MXFP4_PAIR_DIAG_NOSTORE
-                    if (m < 0) {
-#else
-                    if (m < p.M) {
-#endif
-                        if (vec) {
-                            *reinterpret_cast<uint4*>(p.out + (int64_t)m * p.ldo + n0 + seg * 8) = *reinterpret_cast<const uint4*>(t16 + row * 32 + seg * 8);
+                    for (int j = 0; j < 16; j += 2) {
+                        if (has_bias) {
+                            // `output += bias` in bf16: round the product, add, round again
+                            const float a = __bfloat162float(__float2bfloat16_rn(__uint_as_float(v[j]))) + bias;
+                            const float b = __bfloat162float(__float2bfloat16_rn(__uint_as_float(v[j + 1]))) + bias;
+                            const __nv_bfloat162 y = __floats2bfloat162_rn(a, b);
+                            pk[c * 8 + (j >> 1)] = *reinterpret_cast<const uint32_t*>(&y);
                         } else {
-                            for (int x = 0; x < 8; ++x)
-                                if (n0 + seg * 8 + x < p.N) p.out[(int64_t)m * p.ldo + n0 + seg * 8 + x] = t16[row * 32 + seg * 8 + x];
+                            const __nv_bfloat162 y = __floats2bfloat162_rn(__uint_as_float(v[j]), __uint_as_float(v[j + 1]));
+                            pk[c * 8 + (j >> 1)] = *reinterpret_cast<const uint32_t*>(&y);
                         }
                     }
                 }
-                __syncwarp();
-#ifdef MXFP4_PAIR_PROF
-                sb[0] += s1 - s0; sb[1] += s2 - s1; sb[2] += clock64() - s2;
-#endif
-            };
-            uint32_t va[32], vb[32];
-            if (nchunk == 0) {
-                release();
-                continue;
             }
-            // Two blocks are loaded up front and each buffer is refilled as soon as its block has been written out, so the
-            // last tensor-memory load -- and with it the release of the accumulator -- comes two block stores before the end.
-            tc_ld_32x32_nowait(taddr0, va);
-            if (nchunk > 1) tc_ld_32x32_nowait(taddr0 + 32, vb);
-            tc_wait_ld(va);
-            if (nchunk > 1) tc_wait_ld(vb);
-            if (nchunk <= 2) release();
-#pragma unroll 1
-            for (int c = 0; c < nchunk; c += 2) {
-                store_block(va, c);
-                if (c + 2 < nchunk) tc_ld_32x32_nowait(taddr0 + (c + 2) * 32, va);
-                if (c + 1 < nchunk) store_block(vb, c + 1);
-                if (c + 3 < nchunk) tc_ld_32x32_nowait(taddr0 + (c + 3) * 32, vb);
-                if (c + 2 < nchunk) {
-                    tc_wait_ld(va);
-                    if (c + 3 < nchunk) tc_wait_ld(vb);
-                    if (c + 4 >= nchunk) release();        // those were the last loads
+            release();
+            // Phase 2: block by block through the warp's 32 x 32 staging tile (transpose: 32 consecutive n per row) and out
+            unsigned short* t16u = reinterpret_cast<unsigned short*>(t16);
+#pragma unroll
+            for (int c = 0; c < kBlocks; ++c) {
+                if (c < nchunk) {
+                    const int m0 = mbeg + c * 32;
+                    if (p.tma_store) {
+                        // the previous tile must have been read out of shared memory before it is overwritten
+                        if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+                        __syncwarp();
+                    }
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        const uint32_t w2 = pk[c * 16 + j];
+                        t16u[(2 * j) * 32 + lane] = (unsigned short)(w2 & 0xFFFFu);
+                        t16u[(2 * j + 1) * 32 + lane] = (unsigned short)(w2 >> 16);
+                    }
+                    if (p.tma_store) {
+                        // the 32 (m) x 32 (n) bf16 tile leaves as one TMA store; rows and columns past M, N are clipped
+                        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                        __syncwarp();
+                        if (lane == 0 && n0 < p.N) {
+                            asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(&map_out), "r"(smem_u32(t16)),
+                                         "r"(n0), "r"(m0)
+                                         : "memory");
+                            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                        }
+                    } else {
+                        __syncwarp();
+#pragma unroll
+                        for (int r = 0; r < 4; ++r) {
+                            const int row = r * 8 + (lane >> 2), seg = lane & 3;
+                            const int m = m0 + row;
+                            if (m < p.M) {
+                                if (vec) {
+                                    *reinterpret_cast<uint4*>(p.out + (int64_t)m * p.ldo + n0 + seg * 8) = *reinterpret_cast<const uint4*>(t16 + row * 32 + seg * 8);
+                                } else {
+                                    for (int x = 0; x < 8; ++x)
+                                        if (n0 + seg * 8 + x < p.N) p.out[(int64_t)m * p.ldo + n0 + seg * 8 + x] = t16[row * 32 + seg * 8 + x];
+                                }
+                            }
+                        }
+                        __syncwarp();
+                    }
                 }
             }
-            (void)0;
-#ifdef MXFP4_PAIR_PROF
-            if (leader && warp == 6 && lane == 0) {
-                long long* hp = reinterpret_cast<long long*>(p.status) + 1024 + (blockIdx.x + 1) * 8;
-                hp[4] += ep1 - ep0;
-                hp[7] += clock64() - ep1;
-                hp[1] += sb[0]; hp[2] += sb[1]; hp[6] += sb[2];
-            }
-#endif
         }
         if (p.tma_store && lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");     // all tile stores of this warp are complete
         __syncwarp();

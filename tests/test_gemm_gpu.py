@@ -241,3 +241,36 @@ def test_quant_matmul_host_equals_device_path(M, chunk):
         assert torch.equal(got.view(torch.int16), want.view(torch.int16))
     with pytest.raises(ValueError):
         mxfp4.quant_matmul_host(x.to(dev), packed, scales)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("M,N,K,bn", [(512, 256, 256, 256), (1000, 1408, 4128, 256), (600, 264, 512, 192), (2048, 1536, 1024, 128),
+                                       (1536, 4096, 2048, 256)])
+@pytest.mark.parametrize("mode", ["exact", "fast"])
+def test_pair_kernel_equals_one_cta_kernel(monkeypatch, M, N, K, bn, mode):
+    """The cta_group::2 kernel accumulates in the same order as the one-CTA kernel: results are bit-identical, with a
+    bias, for ragged M / N / K, weight-tile counts that leave the second CTA of the last pair without rows, and for
+    an output view whose pitch rules out TMA stores."""
+    import mxfp4
+    from mxfp4 import gemm
+    dev = torch.device("cuda", 0)
+    packed, scales = mxfp4.MXFP4Quantizer(32, "e8m0").quantize(weight(N, K, 3, True).to(dev))
+    x = act(M, K, 11).to(dev)
+    bias = (torch.randn(N, generator=torch.Generator().manual_seed(2)) * 0.1).to(torch.bfloat16).to(dev)
+    old = gemm.get_gemm_mode()
+    gemm.set_gemm_mode(mode)
+    try:
+        monkeypatch.setenv("MXFP4_GEMM_PAIR", "0")
+        want = gemm.quant_matmul_2d(x, packed, scales, bias)
+        monkeypatch.setenv("MXFP4_GEMM_PAIR", "1")
+        monkeypatch.setenv("MXFP4_GEMM_PAIR_BN", str(bn))
+        got = gemm.quant_matmul_2d(x, packed, scales, bias)
+        wide = torch.zeros(M, N + 3, dtype=torch.bfloat16, device=dev)          # pitch not a multiple of 16 bytes
+        gemm.quant_matmul_2d(x, packed, scales, bias, out=wide[:, :N])
+        torch.cuda.synchronize()
+        gemm.check_status()
+    finally:
+        gemm.set_gemm_mode(old)
+    assert torch.equal(got.view(torch.int16), want.view(torch.int16))
+    assert torch.equal(wide[:, :N].contiguous().view(torch.int16), want.view(torch.int16))
+    assert float(wide[:, N:].abs().max()) == 0.0
