@@ -351,7 +351,7 @@ def run_gemm(args, rank, world, local):
     assert int(st[0].item()) == 0, "GEMM kernel reported a timed-out wait"
     pk = peaks()
     fp4_peak = 4.0 * pk["bf16_tflops"]
-    roof = {"bound": "tensor", "kernel": f"gemm_mxf4_kernel [{M}x{N}x{K}], {gemm.get_gemm_mode()} mode",
+    roof = {"bound": "tensor", "kernel": f"gemm_mxf4_pair_kernel<256> [{M}x{N}x{K}], {gemm.get_gemm_mode()} mode" if (gemm.get_gemm_mode() == "exact" and os.environ.get("MXFP4_GEMM_PAIR", "1") != "0") else f"gemm_mxf4_kernel [{M}x{N}x{K}], {gemm.get_gemm_mode()} mode",
             "achieved": flops / (k_ms * 1e-3) / 1e12, "peak": fp4_peak, "unit": "TFLOP/s",
             "peak_source": f"4 x {pk['source']} bf16 cuBLAS burst ({pk['bf16_tflops']} TFLOP/s): MEASURED_PEAKS.json has no FP4 entry",
             "traffic": GEMM_TRAFFIC_BYTES, "kernel_ms": k_ms, "launches_timed": reps}
@@ -377,7 +377,7 @@ def run_gemm(args, rank, world, local):
            "ms_per_step": ms_per_step,
            "config": {"workload": f"quant_matmul: bf16 activations [{M},{K}] x MXFP4 weight [{N},{K}] (Llama-2-7B gate/up shape of the GEMM sweep), "
                                   f"bf16 out, fp32 accumulate, {gemm.get_gemm_mode()} mode; step = activation quantiser + GEMM",
-                      "M": M, "N": N, "K": K, "l2": "two activation/output sets of 247 MB rotate; each step touches more than L2"},
+                      "M": M, "N": N, "K": K, "l2": f"two activation/output sets of {(M * K + M * N) * 2 / 1e6:.0f} MB rotate" + ("; each step touches more than L2" if (M * K + M * N) * 2 > 126e6 else "")},
            "dtype": "fp4 (e2m1) x fp4 with e8m0 block scales, fp32 accumulate", "roofline": roof, "gpu_launches": 2 * args.steps,
            "e2e": {"value": world * flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": M * K * 2, "d2h_bytes_per_step": M * N * 2,
                    "ms_per_step": e2e_ms},
@@ -385,6 +385,49 @@ def run_gemm(args, rank, world, local):
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         res["cpu_baseline"] = cpu_gemm_baseline()
     return res
+
+
+def run_gemm_sweep(args, local):
+    """Kernel-only times of mxfp4_gemm_prequantized over a grid of shapes (current MXFP4_GEMM_MODE / MXFP4_GEMM_PAIR settings)."""
+    import mxfp4
+    from mxfp4 import _capi, gemm
+    dev = torch.device("cuda", local)
+    torch.cuda.set_device(dev)
+    L = _capi.load()
+    ms_part, nk_part = args.sweep.split(":")
+    q = mxfp4.MXFP4Quantizer(32, "e8m0")
+    mode = _capi.GEMM_EXACT if gemm.get_gemm_mode() == "exact" else _capi.GEMM_FAST
+    rows = []
+    for nk in nk_part.split(","):
+        N, K = (int(v) for v in nk.lower().split("x"))
+        packed, scales = q.quantize(weight(N, K, 3).to(dev))
+        prep = gemm.prepared_scales(scales, N, K)
+        for M in (int(v) for v in ms_part.split(",")):
+            x = torch.randn(M, K, generator=torch.Generator().manual_seed(11)).to(torch.bfloat16).to(dev)
+            aq = gemm.act_quantize(x)
+            out = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
+            nsp = L.mxfp4_gemm_splitk_bytes(M, N, K)
+            spl = torch.empty(max(nsp, 16), dtype=torch.uint8, device=dev)
+            st = torch.zeros(1024, dtype=torch.int32, device=dev)
+            sp = torch.cuda.current_stream(dev).cuda_stream
+
+            def kern():
+                rc = L.mxfp4_gemm_prequantized(aq[0].data_ptr(), aq[1].data_ptr(), packed.data_ptr(), prep.data_ptr(), None, out.data_ptr(),
+                                               N, M, N, K, mode, spl.data_ptr(), nsp, st.data_ptr(), sp)
+                assert rc == 0, _capi.last_error()
+            for _ in range(3):
+                kern()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(10):
+                kern()
+            e1.record()
+            torch.cuda.synchronize()
+            assert int(st[0].item()) == 0, "GEMM kernel reported a timed-out wait"
+            us = e0.elapsed_time(e1) / 10 * 1e3
+            rows.append({"M": M, "N": N, "K": K, "kernel_us": round(us, 1), "tflops": round(2.0 * M * N * K / us / 1e6, 0)})
+    return {"sweep": rows, "mode": gemm.get_gemm_mode(), "pair": os.environ.get("MXFP4_GEMM_PAIR", "default")}
 
 
 # ------------------------------------------------------------------------------------------------
@@ -499,7 +542,7 @@ def run_decode(args, rank, world, local):
 
 
 # DRAM traffic of one GEMM launch (dram__bytes_read.sum + dram__bytes_write.sum, one ncu capture; see profiles/)
-GEMM_TRAFFIC_BYTES = 43.42e6 + 135.53e6   # read + write, mean of 3 captured launches of the bench shape (1-pass ncu)
+GEMM_TRAFFIC_BYTES = 46.996e6 + 139.78e6      # dram read + write per launch of the bench shape (ncu, profiles/gemm_mxf4_pair_kernel.md)
 
 
 def main():
@@ -510,6 +553,10 @@ def main():
     ap.add_argument("--workload", default=os.environ.get("MXFP4_BENCH_WORKLOAD", "gemm"), choices=["quantize", "gemm", "stack", "decode"])
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--gemm-shape", default=None, metavar="MxNxK",
+                    help="gemm workload on another shape (profiling captures on a small case); the default is the bench shape")
+    ap.add_argument("--sweep", default=None, metavar="M,M,..:NxK,NxK,..",
+                    help="gemm workload: time only the GEMM kernel (10 launches after 3 warm-ups) for every M x (N,K) and print one JSON line")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 
@@ -533,6 +580,13 @@ def main():
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device (the product has no CPU path); use --impl reference for the CPU baseline")
     rank, world, local = dist_setup(args.gpus)
+    if args.gemm_shape:
+        g = globals()
+        g["GEMM_M"], g["GEMM_N"], g["GEMM_K"] = (int(v) for v in args.gemm_shape.lower().split("x"))
+    if args.sweep:
+        if rank == 0:
+            print(json.dumps(run_gemm_sweep(args, local)))
+        return
     res = {"gemm": run_gemm, "quantize": run_quantize, "stack": run_stack, "decode": run_decode}[args.workload](args, rank, world, local)
     res.update({"n_gpus": world, "steps": args.steps, "warmup": args.warmup, "higher_is_better": True, "scaling": "weak",
                 "vs_baseline": None, "data": "synthetic"})
