@@ -38,6 +38,9 @@ __device__ __forceinline__ int64_t blocked_offset(int64_t row, int64_t kb, int64
 __global__ void __launch_bounds__(256) act_quantize_kernel(const uint8_t* __restrict__ x, int64_t M, int64_t kblocks, int64_t ld_bytes,
                                                            int64_t m_pad, int64_t kstages, uint8_t* __restrict__ packed,
                                                            uint8_t* __restrict__ sf) {
+    // a GEMM launched behind this kernel with programmatic stream serialisation may start its set-up and weight loads now
+    // (it waits for this grid's results with griddepcontrol.wait before it touches them)
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const int64_t kb_pad = kstages * 8;
     const int64_t idx = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
     if (idx >= m_pad * kb_pad) return;

@@ -119,25 +119,27 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_mxf4_kernel(const __grid_con
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
+    // a split-K reduction launched behind this kernel may be scheduled as soon as SMs have room (it waits for this grid)
+    if (threadIdx.x == 0) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer
         if (lane == 0) {
-            uint32_t it = 0;          // running stage counter across units
-            bool ok = true;
-            for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x) {
-                const Unit w = get_unit(p, u);
+            // what = 1: weight tile and weight scales, 2: activation tile and activation scales, 3: both
+            auto issue = [&](const Unit& w, int ks, uint32_t it, int what) -> bool {
+                const int s = it % C::kStages;
+                const uint32_t st = base + s * C::kStageBytes;
                 const int m0 = w.m_tile * BN;
-                for (int ks = w.ks0; ks < w.ks1; ++ks, ++it) {
-                    const int s = it % C::kStages;
+                if (what & 1) {
                     const uint32_t ph = (it / C::kStages) & 1;
-                    if (!mbar_wait(empty_bar(s), ph ^ 1u, abort_flag)) { ok = false; break; }
-                    const uint32_t st = base + s * C::kStageBytes;
+                    if (!mbar_wait(empty_bar(s), ph ^ 1u, abort_flag)) return false;
                     mbar_expect_tx(full_bar(s), C::kTxBytes);
                     mbar_expect_tx(sfld_bar(s), C::kSfTxBytes);
                     tma_load_2d(st, &map_w, full_bar(s), ks * kStageKBytes, w.n_tile * kTileW);
-                    tma_load_2d(st + C::kOffX, &map_x, full_bar(s), ks * kStageKBytes, m0);
                     bulk_load(st + C::kOffSfw, p.sfw + ((int64_t)w.n_tile * p.kstages + ks) * 2048, 2048, sfld_bar(s));
+                }
+                if (what & 2) {
+                    tma_load_2d(st + C::kOffX, &map_x, full_bar(s), ks * kStageKBytes, m0);
 #pragma unroll
                     for (int t = 0; t < C::kXT; ++t) {
                         // 128-row scale groups the tile touches; a second group past the end of the buffer is
@@ -147,6 +149,43 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_mxf4_kernel(const __grid_con
                         bulk_load(st + C::kOffSfx + t * 1024, p.sfx + (grp * p.kstages + ks) * 1024, 1024, sfld_bar(s));
                     }
                 }
+                return true;
+            };
+            uint32_t it = 0;          // running stage counter across units
+            bool ok = true;
+            int u = blockIdx.x;
+            int ks = 0;
+            Unit w = {};
+            if (u < total_units) { w = get_unit(p, u); ks = w.ks0; }
+            auto advance = [&]() {
+                ++it;
+                if (++ks >= w.ks1) {
+                    u += gridDim.x;
+                    if (u < total_units) { w = get_unit(p, u); ks = w.ks0; }
+                }
+            };
+            if (p.pdl) {
+                // The activations come from the kernel in front of this one, which may still be running: fill the
+                // pipeline with the weight side first (it depends on nothing), then wait for that kernel, then add
+                // the activation side of the same stages.
+                const int u_save = u, ks_save = ks;
+                const Unit w_save = w;
+                int npre = 0;
+                while (ok && npre < C::kStages && u < total_units) {
+                    ok = issue(w, ks, it, 1);
+                    advance();
+                    ++npre;
+                }
+                asm volatile("griddepcontrol.wait;" ::: "memory");
+                u = u_save; ks = ks_save; w = w_save; it = 0;
+                for (int j = 0; j < npre && ok; ++j) {
+                    issue(w, ks, it, 2);
+                    advance();
+                }
+            }
+            while (ok && u < total_units) {
+                ok = issue(w, ks, it, 3);
+                advance();
             }
         }
         __syncwarp();
@@ -388,6 +427,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_mxf4_kernel(const __grid_con
 // The order of the sum is fixed, so the result does not depend on scheduling.
 __global__ void __launch_bounds__(256) splitk_reduce_kernel(const float* __restrict__ partial, int ksplit, int64_t M, int64_t N,
                                                             const __nv_bfloat16* __restrict__ bias, __nv_bfloat16* __restrict__ out, int64_t ldo) {
+    asm volatile("griddepcontrol.wait;" ::: "memory");      // the partial sums come from the GEMM grid in front
     const int64_t total = M * N;
     for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
         float acc = 0.0f;
@@ -403,6 +443,7 @@ __global__ void __launch_bounds__(256) splitk_reduce_kernel(const float* __restr
 // ldo % 4 == 0 and an 8-byte-aligned output.
 __global__ void __launch_bounds__(256) splitk_reduce4_kernel(const float4* __restrict__ partial, int ksplit, int64_t M, int64_t N,
                                                              const __nv_bfloat16* __restrict__ bias, __nv_bfloat16* __restrict__ out, int64_t ldo) {
+    asm volatile("griddepcontrol.wait;" ::: "memory");      // the partial sums come from the GEMM grid in front
     const int64_t total4 = M * N / 4;
     for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total4; i += (int64_t)gridDim.x * blockDim.x) {
         float4 acc = __ldcs(partial + i);
@@ -485,8 +526,18 @@ int launch_gemm(const CUtensorMap& mw, const CUtensorMap& mx, GemmParams& p, cud
     p.m_tiles = (p.M + BN - 1) / BN;
     const int64_t units = (int64_t)p.n_tiles * p.m_tiles * p.ksplit;
     const int grid = (int)(units < num_sms() ? units : num_sms());      // persistent: at most one CTA per SM
-    gemm_mxf4_kernel<BN><<<grid, kThreads, C::kSmemBytes, st>>>(mw, mx, p);
-    MXFP4_CHECK_LAUNCH("mxfp4_gemm (tcgen05 kernel)");
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)grid, 1, 1);
+    cfg.blockDim = dim3(kThreads, 1, 1);
+    cfg.dynamicSmemBytes = C::kSmemBytes;
+    cfg.stream = st;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr.val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = p.pdl ? 1 : 0;           // may start while the activation quantiser in front is still running
+    cudaError_t le = cudaLaunchKernelEx(&cfg, gemm_mxf4_kernel<BN>, mw, mx, p);
+    if (le != cudaSuccess) return cuda_fail(le, "mxfp4_gemm (tcgen05 kernel)");
     return MXFP4_OK;
 }
 
@@ -560,7 +611,7 @@ constexpr int kControlBytes = 4096;     // control block: int[0] = status word, 
 
 int gemm_run(const uint8_t* a_packed, const uint8_t* a_sf_blocked, const uint8_t* w_packed, const uint8_t* w_sf_prepared,
              const void* bias_bf16, void* out_bf16, int64_t ldo, int64_t M, int64_t N, int64_t K, int mode, void* splitk_workspace,
-             int64_t splitk_bytes, int* status_dev, void* stream) {
+             int64_t splitk_bytes, int* status_dev, void* stream, bool behind_act_quantize = false) {
     if (M < 0 || N < 0 || K < 0) { set_error("mxfp4_gemm: negative size"); return MXFP4_E_SHAPE; }
     if (M == 0 || N == 0) return MXFP4_OK;
     if (K == 0 || K % 32) { set_error("mxfp4_gemm: K=%lld must be a positive multiple of 32", (long long)K); return MXFP4_E_SHAPE; }
@@ -591,6 +642,7 @@ int gemm_run(const uint8_t* a_packed, const uint8_t* a_sf_blocked, const uint8_t
         p.partial = (float*)splitk_workspace;
     }
     p.exact = mode == MXFP4_GEMM_EXACT; p.status = status_dev;
+    p.pdl = behind_act_quantize && !pair_bn;
     cudaStream_t st = (cudaStream_t)stream;
     p.tma_store = 0;
     if (pair_bn) {
@@ -615,9 +667,20 @@ int gemm_run(const uint8_t* a_packed, const uint8_t* a_sf_blocked, const uint8_t
         int64_t grid = (total + 255) / 256;
         const int64_t cap = (int64_t)num_sms() * 16;
         if (grid > cap) grid = cap;
-        if (vec) splitk_reduce4_kernel<<<(unsigned)grid, 256, 0, st>>>((const float4*)p.partial, p.ksplit, M, N, p.bias, p.out, ldo);
-        else splitk_reduce_kernel<<<(unsigned)grid, 256, 0, st>>>(p.partial, p.ksplit, M, N, p.bias, p.out, ldo);
-        MXFP4_CHECK_LAUNCH("mxfp4_gemm (split-K reduction)");
+        // launched with programmatic stream serialisation: the grid is scheduled while the GEMM drains and waits for it inside
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3((unsigned)grid, 1, 1);
+        cfg.blockDim = dim3(256, 1, 1);
+        cfg.stream = st;
+        cudaLaunchAttribute attr;
+        attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr.val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = &attr;
+        cfg.numAttrs = 1;
+        cudaError_t le;
+        if (vec) le = cudaLaunchKernelEx(&cfg, splitk_reduce4_kernel, (const float4*)p.partial, p.ksplit, M, N, p.bias, p.out, ldo);
+        else le = cudaLaunchKernelEx(&cfg, splitk_reduce_kernel, (const float*)p.partial, p.ksplit, M, N, p.bias, p.out, ldo);
+        if (le != cudaSuccess) return cuda_fail(le, "mxfp4_gemm (split-K reduction)");
     }
     return MXFP4_OK;
 }
@@ -653,7 +716,7 @@ extern "C" int mxfp4_gemm(const void* x_bf16, int64_t ldx, const uint8_t* w_pack
     int rc = mxfp4_act_quantize(x_bf16, M, K, ldx, a_packed, a_sf, stream);
     if (rc) return rc;
     return gemm_run(a_packed, a_sf, w_packed, w_sf_prepared, bias_bf16, out_bf16, ldo, M, N, K, mode, partial,
-                    mxfp4_gemm_splitk_bytes(M, N, K), status, stream);
+                    mxfp4_gemm_splitk_bytes(M, N, K), status, stream, /*behind_act_quantize=*/true);
 }
 
 // ------------------------------------------------------------------------------------------------

@@ -19,6 +19,7 @@ struct GemmParams {
     int ksplit;             // K is cut into this many ranges of whole stages, one work unit each
     int n_tiles, m_tiles;
     int exact;
+    int pdl;                // launched behind the activation quantiser with programmatic stream serialisation
     int* status;
     int tma_store;          // cta_group::2 kernel: the output goes out as TMA tile stores (map_out is valid)
 };
