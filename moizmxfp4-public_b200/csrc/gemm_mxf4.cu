@@ -543,16 +543,51 @@ int launch_gemm(const CUtensorMap& mw, const CUtensorMap& mx, GemmParams& p, cud
 
 inline int64_t align_up(int64_t v, int64_t a) { return (v + a - 1) / a * a; }
 
-// Activation-tile width (the MMA's N): the narrowest tile that covers a small M; for large M, 192 unless its
-// padding wastes more than 4 %.
-int pick_bn(int64_t M) {
-    if (M <= 32) return 32;
-    if (M <= 64) return 64;
-    if (M <= 128) return 128;
-    const int64_t pad256 = (M + 255) / 256 * 256, pad192 = (M + 191) / 192 * 192;
-    if (pad192 * 100 <= M * 104) return 192;      // two accumulators fit: the epilogue overlaps the next unit's MMAs
-    return pad256 * 100 <= M * 104 ? 256 : 128;
+// Tile width (the MMA's N = activation rows per tile) and number of K ranges of the one-CTA kernel, chosen together
+// from a cost model in units of one 128-wide pipeline stage:
+//     rounds * (stages per unit + fixed cost per unit) * t(bn)  [+ reduction: fixed cost + traffic of the partials]
+// with rounds = ceil(tiles * ksplit / SMs) and t(128, 192, 256) = 1, 1.19, 1.375 (shared-memory bytes per stage); a
+// 256-wide tile has a single accumulator, so its epilogue is not hidden and costs three more stages per unit.
+// Problems with fewer tiles than SMs leave most of the chip idle; narrower tiles or a cut along K spread the weight
+// stream over it.  The model was fitted to the measured grid M in {192..1024} x {4096^2, 11008x4096, 4096x11008} and is
+// within ~10 % of the best measured (bn, ksplit) everywhere there.  MXFP4_GEMM_BN / MXFP4_GEMM_KSPLIT override.
+struct TilePlan {
+    int bn, ksplit;
+};
+TilePlan pick_plan(int64_t M, int64_t N, int64_t K) {
+    const int64_t nks = (K + kStageK - 1) / kStageK;
+    const int64_t sms = num_sms();
+    const int64_t n_tiles = (N + kTileW - 1) / kTileW;
+    int force_bn = 0, force_ks = 0;
+    if (const char* e = getenv("MXFP4_GEMM_BN")) {
+        const int v = atoi(e);
+        if (v == 32 || v == 64 || v == 128 || v == 192 || v == 256) force_bn = v;
+    }
+    if (const char* e = getenv("MXFP4_GEMM_KSPLIT")) {
+        const int v = atoi(e);
+        if (v >= 1 && v <= 32) force_ks = v <= nks ? v : (int)nks;
+    }
+    static const int kWidths[5] = {32, 64, 128, 192, 256};
+    static const int kT1000[5] = {700, 800, 1000, 1190, 1375};     // t(bn) x 1000 (narrow tiles: measured, latency-dominated)
+    TilePlan best = {128, 1};
+    int64_t best_cost = -1;
+    for (int i = 0; i < 5; ++i) {
+        const int bn = kWidths[i];
+        if (force_bn ? bn != force_bn : (M <= 128 ? bn != (M <= 32 ? 32 : M <= 64 ? 64 : 128) : bn < 128)) continue;
+        const int64_t tiles = n_tiles * ((M + bn - 1) / bn);
+        const int64_t unit_fixed = bn == 256 ? 5 : 2;
+        for (int ks = 1; ks <= 32 && ks <= nks; ++ks) {
+            if (force_ks ? ks != force_ks : (ks > 1 && (M > 1024 || tiles * 4 >= sms * 3))) continue;
+            const int64_t rounds = (tiles * ks + sms - 1) / sms;
+            int64_t cost = rounds * ((nks + ks - 1) / ks + unit_fixed) * kT1000[i];
+            if (ks > 1) cost += 3000 + (int64_t)ks * M * N * 8 / 5000;       // reduction: launch + partials written and read (~5 MB per stage time)
+            if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = {bn, ks}; }
+        }
+    }
+    return best;
 }
+int pick_bn(int64_t M, int64_t N, int64_t K) { return pick_plan(M, N, K).bn; }
+int pick_ksplit(int64_t M, int64_t N, int64_t K) { return pick_plan(M, N, K).ksplit; }
 
 // Tile width of the cta_group::2 kernel (gemm_mxf4_pair.cu), or 0 for the one-CTA kernel.  Measured on B200 against the
 // one-CTA kernel: in EXACT mode the pair kernel is 5-20 % faster from M = 512 up except for the smallest problems
@@ -568,25 +603,6 @@ int pick_pair_bn(int64_t M, int64_t N, bool exact) {
     const char* b = getenv("MXFP4_GEMM_PAIR_BN");
     const int bn = b ? atoi(b) : 0;
     return (bn == 128 || bn == 192 || bn == 256) ? bn : 256;
-}
-
-// Number of K ranges.  Skinny problems have fewer tiles than SMs; cutting K spreads the weight stream over
-// the whole chip.  Cost model in units of one pipeline stage: rounds * (stages per unit + fixed cost per unit)
-// + a fixed cost for the reduction.
-int pick_ksplit(int64_t M, int64_t N, int64_t K) {
-    const int64_t nks = (K + kStageK - 1) / kStageK;
-    if (M > 128 || nks < 2) return 1;
-    const int64_t tiles = (N + kTileW - 1) / kTileW;     // M <= 128: one activation tile
-    const int64_t sms = num_sms();
-    int best = 1;
-    int64_t best_cost = (tiles + sms - 1) / sms * (nks + 2);
-    for (int ks = 2; ks <= 32 && ks <= nks; ++ks) {
-        const int64_t rounds = (tiles * ks + sms - 1) / sms;
-        // + fixed cost of the reduction + its traffic (partials written and read: ks*M*N*8 bytes, ~5 MB per stage time)
-        const int64_t cost = rounds * ((nks + ks - 1) / ks + 2) + 3 + (int64_t)ks * M * N * 8 / 5000000;
-        if (cost < best_cost) { best_cost = cost; best = ks; }
-    }
-    return best;
 }
 
 }  // namespace
@@ -625,7 +641,7 @@ int gemm_run(const uint8_t* a_packed, const uint8_t* a_sf_blocked, const uint8_t
     }
     CUtensorMap mw, mx;
     const int pair_bn = pick_pair_bn(M, N, mode == MXFP4_GEMM_EXACT);            // 0: one-CTA kernel
-    const int bn = pair_bn ? pair_bn : pick_bn(M);
+    const int bn = pair_bn ? pair_bn : pick_bn(M, N, K);
     int rc = make_map(&mw, w_packed, N, K / 2, kTileW);
     if (rc) return rc;
     rc = make_map(&mx, a_packed, M, K / 2, pair_bn ? pair_bn / 2 : bn);
@@ -636,7 +652,7 @@ int gemm_run(const uint8_t* a_packed, const uint8_t* a_sf_blocked, const uint8_t
     p.ldo = ldo; p.M = (int)M; p.N = (int)N; p.K = (int)K; p.kstages = (int)((K + kStageK - 1) / kStageK);
     p.n_tiles = (int)((N + kTileW - 1) / kTileW); p.m_tiles = 0;
     p.ksplit = 1;
-    const int want = pick_ksplit(M, N, K);
+    const int want = pair_bn ? 1 : pick_ksplit(M, N, K);
     if (want > 1 && splitk_workspace != nullptr && splitk_bytes >= (int64_t)want * M * N * 4 && (uintptr_t)splitk_workspace % 16 == 0) {
         p.ksplit = want;
         p.partial = (float*)splitk_workspace;
