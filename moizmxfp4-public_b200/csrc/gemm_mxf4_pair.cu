@@ -214,6 +214,12 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
     const int total_units = n_pairs * p.m_tiles;
     const int first_unit = blockIdx.x >> 1, unit_step = gridDim.x >> 1;
 
+    if (threadIdx.x == 64) {
+        // fetch the TMA descriptors now: the first loads and stores would otherwise pay for it
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_x) : "memory");
+        if (p.tma_store) asm volatile("prefetch.tensormap [%0];" ::"l"(&map_out) : "memory");
+    }
     if (threadIdx.x == 0) {
         for (int s = 0; s < C::kStages; ++s) {
             mbar_init(full_bar(s), 1);
