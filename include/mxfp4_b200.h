@@ -115,8 +115,8 @@ MXFP4_API int mxfp4_act_quantize(const void* x_bf16, int64_t M, int64_t K, int64
 MXFP4_API int mxfp4_prepare_weight_scales(const uint8_t* scales, int64_t N, int64_t K, uint8_t* prepared, void* stream);
 
 /* Workspace of mxfp4_gemm: 4 KB control block (status word; rest reserved) + packed activations + blocked activation scales + the
- * float32 partial sums of a K-split (mxfp4_gemm_splitk_bytes; skinny problems, M <= 128, are cut along K so that
- * every SM streams part of the weight; the partials are summed in a fixed order by a second kernel). */
+ * float32 partial sums of a K-split (mxfp4_gemm_splitk_bytes; problems with fewer tiles than SMs, M <= 1024, may be
+ * cut along K so that every SM streams part of the weight; the partials are summed in a fixed order by a second kernel). */
 MXFP4_API int64_t mxfp4_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K, int mode);
 MXFP4_API int64_t mxfp4_gemm_splitk_bytes(int64_t M, int64_t N, int64_t K);
 
@@ -130,7 +130,10 @@ MXFP4_API int64_t mxfp4_gemm_splitk_bytes(int64_t M, int64_t N, int64_t K);
  *   workspace      device, >= mxfp4_gemm_workspace_bytes, 256-byte aligned.  Its first 4 KB are a control block that the
  *                  caller zeroes once (not per call): int[0] is a status word -- a kernel whose bounded wait ran out stores
  *                  MXFP4_E_TIMEOUT there -- and the rest is reserved.
- * K % 32 == 0.  Launches two kernels (activation quantiser, GEMM) on `stream`.
+ * K % 32 == 0.  Launches two or three kernels on `stream` (activation quantiser, GEMM, split-K reduction), chained by
+ * programmatic dependent launch: each starts its set-up while the one in front drains and waits for its results on the
+ * device.  Work enqueued on the stream before and after the call is ordered as with plain launches.  Large M in EXACT
+ * mode runs on CTA pairs (tcgen05 cta_group::2, clusters of two); results are bit-identical to the one-CTA kernel.
  */
 MXFP4_API int mxfp4_gemm(const void* x_bf16, int64_t ldx, const uint8_t* w_packed, const uint8_t* w_sf_prepared,
                          const void* bias_bf16, void* out_bf16, int64_t ldo, int64_t M, int64_t N, int64_t K, int mode,
