@@ -245,7 +245,7 @@ def test_quant_matmul_host_equals_device_path(M, chunk):
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("M,N,K,bn", [(512, 256, 256, 256), (1000, 1408, 4128, 256), (600, 264, 512, 192), (2048, 1536, 1024, 128),
-                                       (1536, 4096, 2048, 256)])
+                                       (1536, 4096, 2048, 256), (640, 1001, 288, 256)])
 @pytest.mark.parametrize("mode", ["exact", "fast"])
 def test_pair_kernel_equals_one_cta_kernel(monkeypatch, M, N, K, bn, mode):
     """The cta_group::2 kernel accumulates in the same order as the one-CTA kernel: results are bit-identical, with a
