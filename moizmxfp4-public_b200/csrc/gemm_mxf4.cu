@@ -158,39 +158,55 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_mxf4_kernel(const __grid_con
             };
             uint32_t it = 0;          // running stage counter across units
             bool ok = true;
-            int u = blockIdx.x;
-            int ks = 0;
-            Unit w = {};
-            if (u < total_units) { w = get_unit(p, u); ks = w.ks0; }
-            auto advance = [&]() {
-                ++it;
-                if (++ks >= w.ks1) {
-                    u += gridDim.x;
-                    if (u < total_units) { w = get_unit(p, u); ks = w.ks0; }
-                }
-            };
+            int u_start = blockIdx.x, ks_start = -1;       // where the main loop begins (-1: at the unit's first stage)
             if (p.pdl) {
                 // The activations come from the kernel in front of this one, which may still be running: fill the
                 // pipeline with the weight side first (it depends on nothing), then wait for that kernel, then add
                 // the activation side of the same stages.
-                const int u_save = u, ks_save = ks;
-                const Unit w_save = w;
-                int npre = 0;
+                int u = blockIdx.x, ks = 0, npre = 0;
+                Unit w = {};
+                if (u < total_units) { w = get_unit(p, u); ks = w.ks0; }
+                auto advance = [&]() {
+                    if (++ks >= w.ks1) {
+                        u += gridDim.x;
+                        if (u < total_units) { w = get_unit(p, u); ks = w.ks0; }
+                    }
+                };
                 while (ok && npre < C::kStages && u < total_units) {
-                    ok = issue(w, ks, it, 1);
+                    ok = issue(w, ks, (uint32_t)npre, 1);
                     advance();
                     ++npre;
                 }
+                u_start = u; ks_start = ks;
                 asm volatile("griddepcontrol.wait;" ::: "memory");
-                u = u_save; ks = ks_save; w = w_save; it = 0;
+                u = blockIdx.x;
+                if (u < total_units) { w = get_unit(p, u); ks = w.ks0; }
                 for (int j = 0; j < npre && ok; ++j) {
-                    issue(w, ks, it, 2);
+                    issue(w, ks, (uint32_t)j, 2);
                     advance();
                 }
+                it = (uint32_t)npre;
             }
-            while (ok && u < total_units) {
-                ok = issue(w, ks, it, 3);
-                advance();
+            for (int u = u_start; u < total_units && ok; u += gridDim.x) {
+                const Unit w = get_unit(p, u);
+                const int m0 = w.m_tile * BN;
+                for (int ks = (u == u_start && ks_start >= 0) ? ks_start : w.ks0; ks < w.ks1; ++ks, ++it) {
+                    const int s = it % C::kStages;
+                    const uint32_t ph = (it / C::kStages) & 1;
+                    if (!mbar_wait(empty_bar(s), ph ^ 1u, abort_flag)) { ok = false; break; }
+                    const uint32_t st = base + s * C::kStageBytes;
+                    mbar_expect_tx(full_bar(s), C::kTxBytes);
+                    mbar_expect_tx(sfld_bar(s), C::kSfTxBytes);
+                    tma_load_2d(st, &map_w, full_bar(s), ks * kStageKBytes, w.n_tile * kTileW);
+                    tma_load_2d(st + C::kOffX, &map_x, full_bar(s), ks * kStageKBytes, m0);
+                    bulk_load(st + C::kOffSfw, p.sfw + ((int64_t)w.n_tile * p.kstages + ks) * 2048, 2048, sfld_bar(s));
+#pragma unroll
+                    for (int t = 0; t < C::kXT; ++t) {
+                        int64_t grp = m0 / 128 + t;
+                        if (grp * 128 >= ((int64_t)p.M + 127) / 128 * 128) grp = m0 / 128;
+                        bulk_load(st + C::kOffSfx + t * 1024, p.sfx + (grp * p.kstages + ks) * 1024, 1024, sfld_bar(s));
+                    }
+                }
             }
         }
         __syncwarp();
@@ -552,7 +568,7 @@ inline int64_t align_up(int64_t v, int64_t a) { return (v + a - 1) / a * a; }
 // from a cost model in units of one 128-wide pipeline stage:
 //     rounds * (stages per unit + fixed cost per unit) * t(bn)  [+ reduction: fixed cost + traffic of the partials]
 // with rounds = ceil(tiles * ksplit / SMs) and t(128, 192, 256) = 1, 1.19, 1.375 (shared-memory bytes per stage); a
-// 256-wide tile has a single accumulator, so its epilogue is not hidden and costs three more stages per unit.
+// 256-wide tile has a single accumulator, so its epilogue is not hidden and costs six more stages per unit.
 // Problems with fewer tiles than SMs leave most of the chip idle; narrower tiles or a cut along K spread the weight
 // stream over it.  The model was fitted to the measured grid M in {192..1024} x {4096^2, 11008x4096, 4096x11008} and is
 // within ~10 % of the best measured (bn, ksplit) everywhere there.  MXFP4_GEMM_BN / MXFP4_GEMM_KSPLIT override.
@@ -580,7 +596,7 @@ TilePlan pick_plan(int64_t M, int64_t N, int64_t K) {
         const int bn = kWidths[i];
         if (force_bn ? bn != force_bn : (M <= 128 ? bn != (M <= 32 ? 32 : M <= 64 ? 64 : 128) : bn < 128)) continue;
         const int64_t tiles = n_tiles * ((M + bn - 1) / bn);
-        const int64_t unit_fixed = bn == 256 ? 5 : 2;
+        const int64_t unit_fixed = bn == 256 ? 8 : 2;
         for (int ks = 1; ks <= 32 && ks <= nks; ++ks) {
             if (force_ks ? ks != force_ks : (ks > 1 && (M > 1024 || tiles * 4 >= sms * 3))) continue;
             const int64_t rounds = (tiles * ks + sms - 1) / sms;
