@@ -611,15 +611,17 @@ int pick_bn(int64_t M, int64_t N, int64_t K) { return pick_plan(M, N, K).bn; }
 int pick_ksplit(int64_t M, int64_t N, int64_t K) { return pick_plan(M, N, K).ksplit; }
 
 // Tile width of the cta_group::2 kernel (gemm_mxf4_pair.cu), or 0 for the one-CTA kernel.  Measured on B200 against the
-// one-CTA kernel: in EXACT mode the pair kernel is 5-20 % faster from M = 512 up except for the smallest problems
-// (M <= 1024 with N <= 4096); in FAST mode it wins only up to M = 2048.  MXFP4_GEMM_PAIR=0 forces the one-CTA kernel,
-// MXFP4_GEMM_PAIR=1 the pair kernel wherever it can run; MXFP4_GEMM_PAIR_BN picks the width (128, 192, 256).
+// one-CTA kernel over M in {512..16384} x (N, K) in {4096^2, 11008x4096, 4096x11008, 12288x4096, 22016x4096}: in EXACT mode
+// the pair kernel is 5-20 % faster from M = 768 up (from 512 for very wide weights); in FAST mode it wins only for
+// M = 1024..2048 with N <= 12288.  MXFP4_GEMM_PAIR=0 forces the one-CTA kernel, MXFP4_GEMM_PAIR=1 the pair kernel wherever
+// it can run (M >= 512, N >= 256); MXFP4_GEMM_PAIR_BN picks the width (128, 192, 256).
 int pick_pair_bn(int64_t M, int64_t N, bool exact) {
     const char* e = getenv("MXFP4_GEMM_PAIR");
     const int forced = e ? atoi(e) : -1;
     if (forced == 0 || M < 512 || N < 256) return 0;
     if (forced < 0) {
-        if (exact ? (M <= 1024 && N <= 4096) : (M > 2048)) return 0;
+        const bool use = exact ? (M >= 768 || N >= 16384) : (M >= 1024 && M <= 2048 && N <= 12288);
+        if (!use) return 0;
     }
     const char* b = getenv("MXFP4_GEMM_PAIR_BN");
     const int bn = b ? atoi(b) : 0;
