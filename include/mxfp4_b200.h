@@ -169,6 +169,25 @@ MXFP4_API int mxfp4_gemm_noalloc(const void* x_bf16, int64_t ldx, const uint8_t*
                                  const void* bias_bf16, void* out_bf16, int64_t ldo, int64_t M, int64_t N, int64_t K, int mode,
                                  int* status_dev, void* stream);
 
+/*
+ * Tensor parallelism on one NVSwitch box (no counterpart in the reference, which has no distributed code): sum of the
+ * bf16 partial products [M, N] of a row-parallel layer over `world` ranks, one process per GPU, as ONE kernel over peer
+ * memory (P2P loads and stores; no NCCL call, no multimem).  Every rank adds all partials in float32 in rank order, so
+ * all ranks get the same bits; the bias is added once, after the sum.
+ *   blocks     host array [world] of device pointers: every rank's peer-visible block for this call site (blocks[rank] is
+ *              this rank's own; the others are the peers' blocks as mapped into this process, e.g. torch symmetric
+ *              memory or CUDA IPC).  Layout of a block: mxfp4_peer_partial_offset() bytes of flags, zeroed once before
+ *              the first call on every rank, then the rank's partial, [M, ld] bf16.  The GEMM writes the partial there.
+ *   epoch      local device uint32[2], zeroed once: the call counter of this call site (device-side, so a launch
+ *              captured in a CUDA graph works on every replay).
+ *   status_dev optional local device int: receives MXFP4_E_TIMEOUT if a peer did not show up within about ten seconds.
+ * All ranks must make the same sequence of calls per call site.  N, ld, ldo multiples of 8; world <= 8.
+ */
+MXFP4_API int64_t mxfp4_peer_block_bytes(int64_t M, int64_t ld);
+MXFP4_API int64_t mxfp4_peer_partial_offset(void);
+MXFP4_API int mxfp4_peer_allreduce(void* const* blocks, int world, int rank, uint32_t* epoch, const void* bias_bf16, void* out_bf16,
+                                   int64_t ldo, int64_t M, int64_t N, int64_t ld, int* status_dev, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -63,6 +63,12 @@ def load():
     L.mxfp4_gemm_splitk_bytes.argtypes = [i64, i64, i64]
     L.mxfp4_gemm_splitk_bytes.restype = i64
     L.mxfp4_gemm_prequantized.restype = ci
+    L.mxfp4_peer_block_bytes.argtypes = [i64, i64]
+    L.mxfp4_peer_block_bytes.restype = i64
+    L.mxfp4_peer_partial_offset.argtypes = []
+    L.mxfp4_peer_partial_offset.restype = i64
+    L.mxfp4_peer_allreduce.argtypes = [ctypes.POINTER(vp), ci, ci, vp, vp, vp, i64, i64, i64, i64, vp, vp]
+    L.mxfp4_peer_allreduce.restype = ci
     _lib = L
     return L
 

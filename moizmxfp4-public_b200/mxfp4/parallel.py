@@ -9,15 +9,22 @@ sliced weight: sharding needs no communication and no re-quantisation.
   ColumnParallelMXLinear  weight rows (output features) split over ranks; no collective, the output
                           stays sharded (q, k, v, gate, up, lm_head).
   RowParallelMXLinear     weight columns (input features, K) split over ranks; each rank multiplies its
-                          slice of the activations and one all-reduce (sum, bf16) per layer combines the
-                          partial products (o, down).  The bias is added once, after the reduction.
+                          slice of the activations and the partial products (o, down) are summed over the
+                          ranks.  The bias is added once, after the reduction.  On CUDA the sum is one kernel
+                          of this library over peer memory (mxfp4_peer_allreduce: the GEMM writes its partial
+                          into a peer-visible buffer, every rank reads all of them over NVLink and adds them in
+                          float32 in rank order); NCCL's all-reduce is the fallback (MXFP4_TP_PEER_REDUCE=0,
+                          no symmetric memory, N not a multiple of 8) and the path on CPU (gloo).
 """
+import ctypes
+import os
 from typing import Optional
 
 import torch
 import torch.distributed as dist
 import torch.nn as nn
 
+from . import _capi
 from . import gemm as _gemm
 from .modules import MXLinear
 
@@ -89,6 +96,69 @@ class ColumnParallelMXLinear(_ParallelBase):
         return y
 
 
+class _PeerSum:
+    """Peer-visible partial buffer of one row-parallel call site and the launch of mxfp4_peer_allreduce on it.
+
+    The buffer comes from torch's symmetric memory (every rank allocates the same size and the ranks exchange
+    mappings at rendezvous, a collective: all ranks must reach it in the same order, which SPMD layers do).  It is
+    sized for the largest M seen so far and re-made when a larger M arrives; do the first call at each size outside
+    CUDA graph capture."""
+
+    def __init__(self, group):
+        self.group = group
+        self.rows = 0
+        self.N = 0
+        self.buf = self.handle = self.blocks = self.epoch = self.status = None
+        self.disabled = os.environ.get("MXFP4_TP_PEER_REDUCE", "1") == "0"
+
+    def _make(self, M, N, device):
+        import torch.distributed._symmetric_memory as symm
+        L = _capi.load()
+        rows = max(128, -(-M // 128) * 128)
+        nbytes = L.mxfp4_peer_block_bytes(rows, N)
+        group = self.group if self.group is not None else dist.group.WORLD
+        buf = symm.empty(nbytes, dtype=torch.uint8, device=device)
+        handle = symm.rendezvous(buf, group)
+        buf.zero_()
+        torch.cuda.synchronize(device)
+        dist.barrier(group=group)                      # every rank's flags are zero before anyone signals
+        ptrs = [int(v) for v in handle.buffer_ptrs]
+        self.blocks = (ctypes.c_void_p * len(ptrs))(*ptrs)
+        self.buf, self.handle, self.rows, self.N = buf, handle, rows, N
+        self.epoch = torch.zeros(2, dtype=torch.int32, device=device)
+        self.status = torch.zeros(1, dtype=torch.int32, device=device)
+
+    def partial_view(self, M, N, device):
+        """bf16 [M, N] view of this rank's partial inside the peer-visible block, or None when the peer path is off."""
+        if self.disabled or N % 8:
+            return None
+        if self.buf is None or M > self.rows or N != self.N:
+            try:
+                self._make(M, N, device)
+            except Exception as e:            # no symmetric memory on this system: stay with NCCL
+                self.disabled = True
+                import warnings
+                warnings.warn(f"mxfp4: peer-memory reduction unavailable ({e}); using the NCCL all-reduce")
+                return None
+        off = _capi.load().mxfp4_peer_partial_offset()
+        return self.buf[off:off + M * N * 2].view(torch.bfloat16).view(M, N)
+
+    def reduce(self, M, N, bias, world, rank, device):
+        L = _capi.load()
+        y = torch.empty(M, N, dtype=torch.bfloat16, device=device)
+        b = None if bias is None else bias.to(device=device, dtype=torch.bfloat16).contiguous()
+        with _capi.on_device(device):
+            _capi.check(L.mxfp4_peer_allreduce(self.blocks, world, rank, self.epoch.data_ptr(), None if b is None else b.data_ptr(),
+                                               y.data_ptr(), N, M, N, N, self.status.data_ptr(), _capi.stream_ptr(device)),
+                        "mxfp4_peer_allreduce")
+        return y
+
+    def check_status(self):
+        if self.status is not None and int(self.status.item()) != 0:
+            self.status.zero_()
+            raise _capi.MXFP4BackendError("mxfp4 peer reduction: a rank did not arrive within the wait bound")
+
+
 class RowParallelMXLinear(_ParallelBase):
     """y = all_reduce_sum(x[..., rank slice of K] . W[:, rank slice]^T) + b."""
 
@@ -108,6 +178,17 @@ class RowParallelMXLinear(_ParallelBase):
         k = self.packed_weight.shape[-1] * 2
         if not self.input_is_parallel:
             x = x[..., self.rank * k:(self.rank + 1) * k]
+        if self.world > 1 and x.is_cuda and x.dtype == torch.bfloat16 and x.shape[-1] == k:
+            # GEMM straight into the peer-visible buffer, then one kernel sums all ranks' partials over NVLink
+            if getattr(self, "_peer", None) is None:
+                self._peer = _PeerSum(self.group)
+            x2 = x.reshape(-1, k)
+            M, N = x2.shape[0], self.out_features
+            part = self._peer.partial_view(M, N, x.device) if M > 0 else None
+            if part is not None:
+                _gemm.quant_matmul_2d(x2, self.packed_weight, self.weight_scales, None, out=part)
+                y = self._peer.reduce(M, N, self.bias, self.world, self.rank, x.device)
+                return y.reshape(*x.shape[:-1], N)
         y = _gemm.mxlinear_forward(x, self.packed_weight, self.weight_scales, None, k)
         if self.world > 1:
             y = y.contiguous()

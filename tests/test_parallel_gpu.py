@@ -38,6 +38,36 @@ def _worker(rank, world, port, q):
         ok_col = torch.equal(h, h_full[:, rank * n:(rank + 1) * n])
         y = rp(torch.relu(h))
         err = ((y.float() - full.float()).norm() / full.float().norm()).item()
+        # The row-parallel sum ran as this library's kernel over peer memory.  With two ranks NCCL's bf16 all-reduce rounds
+        # the same float32 sum once, so the two paths must agree bit for bit; the second and third call use the next call
+        # numbers of the device-side epoch, the larger M re-makes the peer buffer, and a CUDA graph replays the launch.
+        ok_peer = getattr(rp, "_peer", None) is not None and not rp._peer.disabled
+        if ok_peer:
+            hin = torch.relu(h)
+            y2 = rp(hin)
+            rp._peer.disabled = True
+            y_nccl = rp(hin)
+            rp._peer.disabled = False
+            ok_peer = torch.equal(y, y2) and (world != 2 or torch.equal(y, y_nccl))
+            big = torch.relu(cp(conftest.act(640, 4096, 6).to(dev)))
+            yb = rp(big)
+            rp._peer.disabled = True
+            yb_nccl = rp(big)
+            rp._peer.disabled = False
+            ok_peer = ok_peer and (world != 2 or torch.equal(yb, yb_nccl))
+            g = torch.cuda.CUDAGraph()
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                rp(hin)
+                torch.cuda.synchronize()
+                with torch.cuda.graph(g, stream=side):
+                    yg = rp(hin)
+            for _ in range(3):
+                g.replay()
+            torch.cuda.synchronize()
+            ok_peer = ok_peer and torch.equal(yg, y)
+            rp._peer.check_status()
         xin = conftest.act(16, 4096, 9).to(dev)
         stack = MXBlockStack.build(n_layers=2, device=dev)
         out = stack(xin)
@@ -49,7 +79,7 @@ def _worker(rank, world, port, q):
         ref = [torch.empty_like(out) for _ in range(world)]
         dist.all_gather(ref, out)
         same = all(torch.equal(ref[0], r) for r in ref)           # every rank ends with the same replicated activations
-        q.put((rank, ok_col and err < 1e-2 and fin and same, err))
+        q.put((rank, ok_col and ok_peer and err < 1e-2 and fin and same, err))
     finally:
         dist.destroy_process_group()
 
