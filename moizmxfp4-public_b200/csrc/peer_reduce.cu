@@ -31,12 +31,9 @@ __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
     asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
     return v;
 }
-// 16 bytes from (possibly peer) memory, not through L1 (the data changes between launches)
-__device__ __forceinline__ uint4 ld_volatile_16(const void* p) {
-    uint4 v;
-    asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
-    return v;
-}
+// 16 bytes from (possibly peer) memory, cached at most in L2 (the data changes between launches; L1 could be stale).
+// Not volatile: the compiler is free to put many of these loads in flight before the first use.
+__device__ __forceinline__ uint4 ld_cg_16(const void* p) { return __ldcg(reinterpret_cast<const uint4*>(p)); }
 
 struct PeerParams {
     uint8_t* block[kMaxWorld];   // every rank's peer-visible block (block[rank] is local)
@@ -60,6 +57,8 @@ __device__ __forceinline__ bool wait_all(const uint32_t* mine, int world, int ra
     return true;
 }
 
+// U vectors of 8 bf16 per thread and iteration, all loads of all ranks issued before the first add
+template <int U>
 __global__ void __launch_bounds__(256) peer_allreduce_kernel(const PeerParams p) {
     __shared__ int s_ok;
     const uint32_t n = p.epoch[0] + 1;                          // stable: only the last block of a launch advances it, at its end
@@ -73,30 +72,49 @@ __global__ void __launch_bounds__(256) peer_allreduce_kernel(const PeerParams p)
     if (s_ok) {
         const int64_t vec_per_row = p.N / 8;
         const int64_t total = p.M * vec_per_row;
-        for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
-            const int64_t m = i / vec_per_row, c = (i - m * vec_per_row) * 8;
-            float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-            for (int r = 0; r < p.world; ++r) {
-                const __nv_bfloat16* src = reinterpret_cast<const __nv_bfloat16*>(p.block[r] + 2 * kMaxWorld * 4) + m * p.ld + c;
-                const uint4 v = ld_volatile_16(src);
-                const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+        const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+        for (int64_t i0 = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i0 < total; i0 += stride * U) {
+            uint4 v[U][kMaxWorld];
+            int64_t off_in[U], off_out[U];
+            int col[U];
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const int64_t i = i0 + u * stride;
+                const int64_t m = i / vec_per_row, c = (i - m * vec_per_row) * 8;
+                off_in[u] = m * p.ld + c; off_out[u] = m * p.ldo + c; col[u] = (int)c;
+                if (i < total) {
+#pragma unroll
+                    for (int r = 0; r < kMaxWorld; ++r)
+                        if (r < p.world) v[u][r] = ld_cg_16(reinterpret_cast<const __nv_bfloat16*>(p.block[r] + 2 * kMaxWorld * 4) + off_in[u]);
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                if (i0 + u * stride >= total) break;
+                float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#pragma unroll
+                for (int r = 0; r < kMaxWorld; ++r) {
+                    if (r < p.world) {
+                        const uint32_t w[4] = {v[u][r].x, v[u][r].y, v[u][r].z, v[u][r].w};
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            acc[2 * j] += __uint_as_float(w[j] << 16);
+                            acc[2 * j + 1] += __uint_as_float(w[j] & 0xFFFF0000u);
+                        }
+                    }
+                }
+                uint32_t o[4];
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
-                    acc[2 * j] += __uint_as_float(w[j] << 16);
-                    acc[2 * j + 1] += __uint_as_float(w[j] & 0xFFFF0000u);
+                    __nv_bfloat16 a = __float2bfloat16_rn(acc[2 * j]), b = __float2bfloat16_rn(acc[2 * j + 1]);
+                    if (p.bias) {
+                        a = __float2bfloat16_rn(__bfloat162float(a) + __bfloat162float(p.bias[col[u] + 2 * j]));
+                        b = __float2bfloat16_rn(__bfloat162float(b) + __bfloat162float(p.bias[col[u] + 2 * j + 1]));
+                    }
+                    o[j] = (uint32_t)__bfloat16_as_ushort(a) | ((uint32_t)__bfloat16_as_ushort(b) << 16);
                 }
+                *reinterpret_cast<uint4*>(p.out + off_out[u]) = make_uint4(o[0], o[1], o[2], o[3]);
             }
-            uint32_t o[4];
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                __nv_bfloat16 a = __float2bfloat16_rn(acc[2 * j]), b = __float2bfloat16_rn(acc[2 * j + 1]);
-                if (p.bias) {
-                    a = __float2bfloat16_rn(__bfloat162float(a) + __bfloat162float(p.bias[c + 2 * j]));
-                    b = __float2bfloat16_rn(__bfloat162float(b) + __bfloat162float(p.bias[c + 2 * j + 1]));
-                }
-                o[j] = (uint32_t)__bfloat16_as_ushort(a) | ((uint32_t)__bfloat16_as_ushort(b) << 16);
-            }
-            *reinterpret_cast<uint4*>(p.out + m * p.ldo + c) = make_uint4(o[0], o[1], o[2], o[3]);
         }
     } else if (threadIdx.x == 0 && p.status) {
         atomicExch(p.status, MXFP4_E_TIMEOUT);
@@ -146,9 +164,12 @@ extern "C" int mxfp4_peer_allreduce(void* const* blocks, int world, int rank, ui
     p.ldo = ldo; p.M = M; p.N = N; p.ld = ld; p.status = status_dev;
     const int64_t total = M * (N / 8);
     int64_t grid = (total + 255) / 256;
-    const int64_t cap = num_sms();            // every block spins on the flags: keep them all resident
+    const int64_t cap = (int64_t)num_sms() * 4;
     if (grid > cap) grid = cap;
-    peer_allreduce_kernel<<<(unsigned)grid, 256, 0, (cudaStream_t)stream>>>(p);
+    // more vectors per thread while few ranks leave registers for them
+    if (world <= 2) peer_allreduce_kernel<4><<<(unsigned)grid, 256, 0, (cudaStream_t)stream>>>(p);
+    else if (world <= 4) peer_allreduce_kernel<2><<<(unsigned)grid, 256, 0, (cudaStream_t)stream>>>(p);
+    else peer_allreduce_kernel<1><<<(unsigned)grid, 256, 0, (cudaStream_t)stream>>>(p);
     MXFP4_CHECK_LAUNCH("mxfp4_peer_allreduce");
     return MXFP4_OK;
 }
