@@ -15,13 +15,15 @@
 //      overwrite this rank's partial.
 // Every wait is bounded (about ten seconds of clock64: ranks of a job may be seconds apart, a lost rank must not hang the
 // others); a wait that runs out sets the status word and the launch finishes.
+#include <cstdlib>
+
 #include "mxfp4_common.cuh"
 
 namespace mxfp4 {
 namespace {
 
 constexpr int kMaxWorld = 8;
-constexpr long long kPeerWaitLimitCycles = 20000000000ll;   // about ten seconds: ranks of one job can be seconds apart
+constexpr long long kPeerWaitDefaultMs = 10000;   // ranks of one job can be seconds apart; MXFP4_PEER_WAIT_MS overrides
 
 __device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
     asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
@@ -43,15 +45,16 @@ struct PeerParams {
     __nv_bfloat16* out;
     int64_t ldo, M, N, ld;       // ld: row pitch of the partials, elements
     int* status;
+    long long wait_cycles;       // bound of each wait
 };
 
 // waits until every peer's counter in `mine[0..world)` has reached n; false when the bound ran out
-__device__ __forceinline__ bool wait_all(const uint32_t* mine, int world, int rank, uint32_t n) {
+__device__ __forceinline__ bool wait_all(const uint32_t* mine, int world, int rank, uint32_t n, long long limit) {
     const long long t0 = clock64();
     for (int r = 0; r < world; ++r) {
         if (r == rank) continue;
         while ((int32_t)(ld_acquire_sys(mine + r) - n) < 0) {
-            if (clock64() - t0 > kPeerWaitLimitCycles) return false;
+            if (clock64() - t0 > limit) return false;
         }
     }
     return true;
@@ -67,7 +70,7 @@ __global__ void __launch_bounds__(256) peer_allreduce_kernel(const PeerParams p)
         __threadfence_system();
         st_release_sys(reinterpret_cast<uint32_t*>(p.block[threadIdx.x]) + p.rank, n);     // ready[rank] in the peer's block
     }
-    if (threadIdx.x == 0) s_ok = wait_all(my_flags, p.world, p.rank, n) ? 1 : 0;
+    if (threadIdx.x == 0) s_ok = wait_all(my_flags, p.world, p.rank, n, p.wait_cycles) ? 1 : 0;
     __syncthreads();
     if (s_ok) {
         const int64_t vec_per_row = p.N / 8;
@@ -127,7 +130,7 @@ __global__ void __launch_bounds__(256) peer_allreduce_kernel(const PeerParams p)
         if (ticket == gridDim.x - 1) {
             for (int r = 0; r < p.world; ++r)
                 if (r != p.rank) st_release_sys(reinterpret_cast<uint32_t*>(p.block[r]) + kMaxWorld + p.rank, n);   // done[rank] in the peer's block
-            if (!wait_all(my_flags + kMaxWorld, p.world, p.rank, n) && p.status) atomicExch(p.status, MXFP4_E_TIMEOUT);
+            if (!wait_all(my_flags + kMaxWorld, p.world, p.rank, n, p.wait_cycles) && p.status) atomicExch(p.status, MXFP4_E_TIMEOUT);
             p.epoch[1] = 0;
             __threadfence();
             p.epoch[0] = n;
@@ -162,6 +165,9 @@ extern "C" int mxfp4_peer_allreduce(void* const* blocks, int world, int rank, ui
     }
     p.world = world; p.rank = rank; p.epoch = epoch; p.bias = (const __nv_bfloat16*)bias_bf16; p.out = (__nv_bfloat16*)out_bf16;
     p.ldo = ldo; p.M = M; p.N = N; p.ld = ld; p.status = status_dev;
+    long long ms = kPeerWaitDefaultMs;
+    if (const char* e = getenv("MXFP4_PEER_WAIT_MS")) { const long long v = atoll(e); if (v > 0 && v <= 600000) ms = v; }
+    p.wait_cycles = ms * 2000000ll;          // clock64 ticks at about 2 GHz
     const int64_t total = M * (N / 8);
     int64_t grid = (total + 255) / 256;
     const int64_t cap = (int64_t)num_sms() * 4;
