@@ -277,10 +277,12 @@ def test_pair_kernel_equals_one_cta_kernel(monkeypatch, M, N, K, bn, mode):
 
 
 @pytest.mark.gpu
-def test_peer_allreduce_single_gpu_and_bounded_wait(monkeypatch):
-    """mxfp4_peer_allreduce with both 'ranks' emulated by buffers of one GPU.  First the peer's flags are set by hand, as its
-    launch would set them: the sum must equal the float32 sum of the two partials plus bias.  Then nothing sets them: the
-    bounded wait runs out, the status word receives MXFP4_E_TIMEOUT and the context stays usable (no fault, no hang)."""
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_peer_allreduce_single_gpu_and_bounded_wait(monkeypatch, world):
+    """mxfp4_peer_allreduce with all 'ranks' emulated by buffers of one GPU (rank 0 runs; the others are data).  First the
+    peers' flags are set by hand, as their launches would set them: the result must be the float32 sum of the partials in
+    rank order, rounded once, plus the bias.  Then nothing sets them: the bounded wait runs out, the status word receives
+    MXFP4_E_TIMEOUT and the context stays usable (no fault, no hang)."""
     import ctypes
     from mxfp4 import _capi
     L = _capi.load()
@@ -288,29 +290,37 @@ def test_peer_allreduce_single_gpu_and_bounded_wait(monkeypatch):
     M, N = 96, 256
     off = L.mxfp4_peer_partial_offset()
     nbytes = L.mxfp4_peer_block_bytes(M, N)
-    blocks = [torch.zeros(nbytes, dtype=torch.uint8, device=dev) for _ in range(2)]
-    parts = [act(M, N, 70 + r).to(dev) for r in range(2)]
+    blocks = [torch.zeros(nbytes, dtype=torch.uint8, device=dev) for _ in range(world)]
+    parts = [act(M, N, 70 + r).to(dev) for r in range(world)]
     for b, p_ in zip(blocks, parts):
         b[off:off + M * N * 2].view(torch.bfloat16).view(M, N).copy_(p_)
     bias = (torch.randn(N, generator=torch.Generator().manual_seed(3)) * 0.1).to(torch.bfloat16).to(dev)
-    arr = (ctypes.c_void_p * 2)(blocks[0].data_ptr(), blocks[1].data_ptr())
+    arr = (ctypes.c_void_p * world)(*[b.data_ptr() for b in blocks])
     epoch = torch.zeros(2, dtype=torch.int32, device=dev)
     status = torch.zeros(1, dtype=torch.int32, device=dev)
     out = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
     flags0 = blocks[0][:off].view(torch.int32)
-    flags0[1] = 1          # ready[1] = 1: rank 1's partial of call 1 is complete
-    flags0[8 + 1] = 1      # done[1] = 1: rank 1 has finished reading call 1
+    for r in range(1, world):
+        flags0[r] = 1          # ready[r] = 1: rank r's partial of call 1 is complete
+        flags0[8 + r] = 1      # done[r] = 1: rank r has finished reading call 1
     monkeypatch.setenv("MXFP4_PEER_WAIT_MS", "200")
-    rc = L.mxfp4_peer_allreduce(arr, 2, 0, epoch.data_ptr(), bias.data_ptr(), out.data_ptr(), N, M, N, N, status.data_ptr(), None)
+    rc = L.mxfp4_peer_allreduce(arr, world, 0, epoch.data_ptr(), bias.data_ptr(), out.data_ptr(), N, M, N, N, status.data_ptr(), None)
     assert rc == 0, _capi.last_error()
     torch.cuda.synchronize()
-    want = ((parts[0].float() + parts[1].float()).to(torch.bfloat16).float() + bias.float()).to(torch.bfloat16)
+    acc = torch.zeros(M, N, dtype=torch.float32, device=dev)
+    for p_ in parts:
+        acc = acc + p_.float()                                   # rank order, float32
+    want = (acc.to(torch.bfloat16).float() + bias.float()).to(torch.bfloat16)
     assert int(status.item()) == 0 and int(epoch[0].item()) == 1 and int(epoch[1].item()) == 0
     assert torch.equal(out.view(torch.int16), want.view(torch.int16))
-    assert int(blocks[1][:off].view(torch.int32)[0].item()) == 1          # rank 0 published ready = 1 in the peer's block
+    for r in range(1, world):                                    # rank 0 published ready = done = 1 in every peer's block
+        fl = blocks[r][:off].view(torch.int32)
+        assert int(fl[0].item()) == 1 and int(fl[8].item()) == 1
+    if world != 2:
+        return
     # call 2: the peer never arrives
     out.zero_()
-    rc = L.mxfp4_peer_allreduce(arr, 2, 0, epoch.data_ptr(), bias.data_ptr(), out.data_ptr(), N, M, N, N, status.data_ptr(), None)
+    rc = L.mxfp4_peer_allreduce(arr, world, 0, epoch.data_ptr(), bias.data_ptr(), out.data_ptr(), N, M, N, N, status.data_ptr(), None)
     assert rc == 0
     torch.cuda.synchronize()
     assert int(status.item()) == -6                            # MXFP4_E_TIMEOUT
