@@ -92,11 +92,6 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_mxf4_kernel(const __grid_con
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int total_units = p.n_tiles * p.m_tiles * p.ksplit;
 
-    if (threadIdx.x == 32) {
-        // fetch the TMA descriptors now: the first loads would otherwise pay for it
-        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
-        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_x) : "memory");
-    }
     if (threadIdx.x == 0) {
         for (int s = 0; s < C::kStages; ++s) {
             mbar_init(full_bar(s), 1);
