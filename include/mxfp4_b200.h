@@ -181,7 +181,7 @@ MXFP4_API int mxfp4_gemm_noalloc(const void* x_bf16, int64_t ldx, const uint8_t*
  *   epoch      local device uint32[2], zeroed once: the call counter of this call site (device-side, so a launch
  *              captured in a CUDA graph works on every replay).
  *   status_dev optional local device int: receives MXFP4_E_TIMEOUT if a peer did not show up within the wait bound (ten
- *              seconds; MXFP4_PEER_WAIT_MS in the environment sets another).  The launch then ends without summing.
+ *              seconds; MXFP4_PEER_WAIT_MS in the environment sets another).  The launch then writes NaN to `out` instead of a sum.
  * All ranks must make the same sequence of calls per call site.  N, ld, ldo multiples of 8; world <= 8.
  */
 MXFP4_API int64_t mxfp4_peer_block_bytes(int64_t M, int64_t ld);

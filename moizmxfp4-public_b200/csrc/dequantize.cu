@@ -22,6 +22,7 @@ __device__ __forceinline__ float decode_mul(unsigned nib, float scale) {
 template <bool kBf16Out>
 __global__ void __launch_bounds__(256) dequantize_e8m0_b32_kernel(const uint32_t* __restrict__ packed, const uint8_t* __restrict__ scales,
                                                                    int64_t nwords, void* __restrict__ out) {
+    MXFP4_CHAIN_PROLOGUE();
     const int64_t stride = (int64_t)gridDim.x * blockDim.x;
     for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < nwords; i += stride) {
         const uint32_t w = __ldg(packed + i);
@@ -108,11 +109,13 @@ extern "C" int mxfp4_dequantize(const uint8_t* packed, const void* scales, int s
         const int64_t nwords = nbytes / 4;
         int64_t grid = (nwords + threads - 1) / threads;
         if (grid > cap) grid = cap;
+        // chained to the kernel in front (see launch_chained): consecutive launches lose the gap between them
+        cudaError_t le;
         if (out_dtype == MXFP4_DT_F32)
-            dequantize_e8m0_b32_kernel<false><<<(unsigned)grid, threads, 0, st>>>((const uint32_t*)packed, (const uint8_t*)scales, nwords, out);
+            le = launch_chained(dequantize_e8m0_b32_kernel<false>, (unsigned)grid, threads, st, (const uint32_t*)packed, (const uint8_t*)scales, nwords, out);
         else
-            dequantize_e8m0_b32_kernel<true><<<(unsigned)grid, threads, 0, st>>>((const uint32_t*)packed, (const uint8_t*)scales, nwords, out);
-        MXFP4_CHECK_LAUNCH("mxfp4_dequantize (streaming kernel)");
+            le = launch_chained(dequantize_e8m0_b32_kernel<true>, (unsigned)grid, threads, st, (const uint32_t*)packed, (const uint8_t*)scales, nwords, out);
+        if (le != cudaSuccess) return cuda_fail(le, "mxfp4_dequantize (streaming kernel)");
         return MXFP4_OK;
     }
     int64_t grid = (nbytes + threads - 1) / threads;

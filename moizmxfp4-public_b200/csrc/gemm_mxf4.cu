@@ -16,7 +16,8 @@
 // MMA's N / TMEM columns) tile of out^T.  K advances in stages of 256 elements (128 bytes per row,
 // one 128-byte swizzle span), 4 MMAs of K=64 per stage and pass.  The grid is persistent (one CTA per SM)
 // and walks a list of work units (K range, weight tile, activation tile).
-// Warps: 0 = TMA producer, 1 = MMA issuer (owns TMEM), 2..5 = correction transform, 6..9 = epilogue.
+// Warps (17): 0 = TMA producer, 1 and 15 = MMA issuers (1 owns TMEM), 2..5 and 11..14 = correction transform,
+// 6..9 = epilogue, 10 and 16 = scale-factor copiers.
 // Every wait is bounded; a wait that runs out records MXFP4_E_TIMEOUT in the status word and the
 // CTA drains and exits.
 #include <cstdlib>
@@ -676,7 +677,7 @@ int gemm_run(const uint8_t* a_packed, const uint8_t* a_sf_blocked, const uint8_t
         p.partial = (float*)splitk_workspace;
     }
     p.exact = mode == MXFP4_GEMM_EXACT; p.status = status_dev;
-    p.pdl = behind_act_quantize && !pair_bn;
+    p.pdl = behind_act_quantize;
     cudaStream_t st = (cudaStream_t)stream;
     p.tma_store = 0;
     if (pair_bn) {
@@ -807,5 +808,5 @@ extern "C" int mxfp4_gemm_noalloc(const void* x_bf16, int64_t ldx, const uint8_t
     int rc = mxfp4_act_quantize(x_bf16, M, K, ldx, a_packed, a_sf, stream);
     if (rc) return rc;
     return gemm_run(a_packed, a_sf, w_packed, w_sf_prepared, bias_bf16, out_bf16, ldo, M, N, K, mode,
-                    split_bytes ? partial : nullptr, split_bytes, status_dev, stream);
+                    split_bytes ? partial : nullptr, split_bytes, status_dev, stream, /*behind_act_quantize=*/true);
 }

@@ -51,29 +51,9 @@ __device__ __forceinline__ void mbar_arrive_remote(uint32_t cluster_addr) {
 __device__ __forceinline__ void mbar_report_remote(uint32_t cluster_addr) {
     mbar_arrive_remote(cluster_addr);
 }
-__device__ __forceinline__ bool mbar_try_wait_cl(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    return ok != 0;
-}
-// bounded wait on a barrier that the other CTA of the pair may signal
+// bounded wait on a barrier that the other CTA of the pair may signal (a local barrier all the same)
 __device__ __forceinline__ bool mbar_wait_cl(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
-    const long long t0 = clock64();
-    for (uint32_t it = 1;; ++it) {
-        if (mbar_try_wait_cl(bar, parity)) return true;
-        if ((it & 63u) == 0) {
-            if (*abort_flag) return false;
-            if (clock64() - t0 > kWaitLimitCycles) break;
-        }
-    }
-    *abort_flag = 1;
-    return false;
+    return mbar_wait(bar, parity, abort_flag);
 }
 __device__ __forceinline__ void cluster_sync_all() {
     asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
@@ -104,10 +84,23 @@ __device__ __forceinline__ uint32_t make_idesc_pair(int n, uint32_t sf_id) {
     return (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | (1u << 23) | ((uint32_t)(256 >> 4) << 24) | (sf_id << 29) | (sf_id << 4);
 }
 
-// warps: 0 TMA producer, 1 and 15 MMA issuers (leader CTA), 2-5 scale-factor writers (one per tensor-memory lane
-// quarter), 6-9 and 19-22 epilogue (two warps per lane quarter, half of the columns each), 10-14 and 16-18
+// warps: 0 TMA producer, 1 and kMma2Warp MMA issuers (leader CTA), 2-5 scale-factor writers (one per tensor-memory lane
+// quarter), 6-9 and kEpi2Warp.. epilogue (two warps per lane quarter, half of the columns each), 10..10+kTransformWarps-1
 // correction transform (EXACT mode)
-constexpr int kPairThreads = 736;
+// Measured on the 8192 x 11008 x 4096 problem, sustained: the second MMA issuer on warp 18 instead of warp 15 (another
+// warp scheduler than before: the two issuers and the producer now sit on three different schedulers) +2.5 %; 4
+// transform warps instead of 8 -1 %; 16 epilogue warps (64 columns each) +1.6 % but they need the shared memory of the
+// third correction tile, which costs 3.5 %; 32-column tensor-memory loads in the epilogue -1 % (spills); a suspend-time
+// hint on mbarrier.try_wait (fewer polling instructions) -1 %.
+constexpr int kTransformWarps = 8;
+constexpr int kEpiWarps = 8;                         // two per lane quarter
+constexpr int kEpiGroups = kEpiWarps / 4;            // column groups of the accumulator, one warp per lane quarter each
+constexpr int kMma2Warp = 10 + kTransformWarps;
+constexpr int kEpi2Warp = kMma2Warp + 1;
+constexpr int kPairThreads = (kEpi2Warp + kEpiWarps - 4) * 32;
+static_assert(kEpiWarps == 8 || kEpiWarps == 16, "epilogue warps");
+static_assert(kTransformWarps == 4 || kTransformWarps == 8, "transform warps");
+static_assert((kEpi2Warp & 3) != ((kEpi2Warp + 1) & 3), "lane quarters");
 
 // 32 lanes x 32 bits, N consecutive columns, registers -> tensor memory
 __device__ __forceinline__ void tc_st_x16(uint32_t taddr, const uint4& a, const uint4& b, const uint4& c, const uint4& d) {
@@ -144,7 +137,8 @@ struct PairCfg {
     static constexpr int kStageBytes = kWBytes + kXBytes;          // a pipeline slot holds the two operand tiles only
     static constexpr int kCorrBufs = 3;                            // ring of correction tiles (EXACT mode)
     static constexpr int kCorrBytes = kCorrBufs * kWBytes;
-    static constexpr int kEpiBytes = 8 * 2048;                     // per epilogue warp: 32 x 32 bf16 for the transpose
+    static constexpr int kEpiBytes = kEpiWarps * 2048;             // per epilogue warp: 32 x 32 bf16 for the transpose
+    static constexpr int kEpiCols = BN / kEpiGroups;               // accumulator columns one epilogue warp drains
     static constexpr int kAccBufs = BN <= 192 ? 2 : 1;
     static constexpr int kAccStride = BN <= 128 ? 128 : (BN <= 192 ? 192 : 256);
     // tensor memory: the accumulators, then a ring of scale-factor column sets
@@ -162,7 +156,7 @@ struct PairCfg {
     static constexpr uint32_t kTxBytes = kWBytes + kXBytes;
     static constexpr int kSfRegs = 4 + 2 * kXT;    // 128-bit words of scale factors a thread moves per stage
     static constexpr int kTmemCols = 512;
-    static_assert(BN % 32 == 0 && BN <= 256 && kHalf % 8 == 0, "tile width");
+    static_assert(BN % 32 == 0 && BN <= 256 && kHalf % 8 == 0 && (BN / kEpiGroups) % 32 == 0, "tile width");
     static_assert(kStages >= 2 && kSfSets >= 2 && 16 + 8 * kXT <= kSfSetCols && kStageBytes % 1024 == 0, "pipeline depth / tensor memory");
 };
 
@@ -225,7 +219,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
             mbar_init(full_bar(s), 1);
             mbar_init(empty_bar(s), 1);
             mbar_init(tiles_bar(s), 1);
-            mbar_init(ready_bar(s), 16);          // 8 + 8 transform warps
+            mbar_init(ready_bar(s), 2 * kTransformWarps);   // the transform warps of both CTAs
         }
         for (int c = 0; c < C::kCorrBufs; ++c) mbar_init(corr_empty_bar(c), 1);
         for (int k = 0; k < C::kSfSets; ++k) {
@@ -234,7 +228,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(acc_full_bar(b), 2);        // both MMA issuers commit (multicast to both CTAs)
-            mbar_init(acc_empty_bar(b), 16);      // 8 epilogue warps in each CTA
+            mbar_init(acc_empty_bar(b), 2 * kEpiWarps);      // the epilogue warps of both CTAs
         }
         mbar_init(unit_started_bar(0), 1);
         mbar_init(unit_started_bar(1), 1);
@@ -260,6 +254,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
             uint32_t it = 0;
             bool ok = true;
             const uint32_t tiles0 = map_to_cta(tiles_bar(0), 0);
+            // launched behind the activation quantiser with programmatic stream serialisation: everything up to here
+            // (barriers, tensor memory, descriptors) overlapped its tail; its results are needed from here on
+            if (p.pdl) asm volatile("griddepcontrol.wait;" ::: "memory");
             for (int u = first_unit; u < total_units && ok; u += unit_step) {
                 const PairUnit w = get_pair_unit(p, n_pairs, u);
                 const int m0 = w.m_tile * BN;
@@ -285,7 +282,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
             }
         }
         __syncwarp();
-    } else if (warp == 1 || warp == 15) {
+    } else if (warp == 1 || warp == kMma2Warp) {
         // ------------------------------------------------------------------ MMA issuers (leader CTA only), alternate stages
         if (leader && lane == 0) {
             const uint32_t me = warp == 1 ? 0u : 1u;
@@ -340,10 +337,11 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
             }
         }
         __syncwarp();
-    } else if (warp >= 10 && warp < 19) {
-        // ------------------------------------------------------------------ correction transform (EXACT mode), 8 warps per CTA
+    } else if (warp >= 10 && warp < kMma2Warp) {
+        // ------------------------------------------------------------------ correction transform (EXACT mode)
         if (p.exact) {
-            const int t = (warp < 15 ? warp - 10 : warp - 11) * 32 + lane;       // warps 10-14 -> 0-4, 16-18 -> 5-7
+            constexpr int kTT = kTransformWarps * 32;                             // transform threads
+            const int t = (warp - 10) * 32 + lane;
             uint32_t it = 0;
             bool ok = true;
             for (int u = first_unit; u < total_units && ok; u += unit_step) {
@@ -356,15 +354,15 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
                     if (!ok) break;
                     const uint4* src = reinterpret_cast<const uint4*>(base_ptr + s * C::kStageBytes);
                     uint4* dst = reinterpret_cast<uint4*>(corr_ptr + cb * C::kWBytes);
-                    uint4 v[C::kWBytes / 16 / 256];
+                    uint4 v[C::kWBytes / 16 / kTT];
 #pragma unroll
-                    for (int j = 0; j < C::kWBytes / 16 / 256; ++j) v[j] = src[j * 256 + t];
+                    for (int j = 0; j < C::kWBytes / 16 / kTT; ++j) v[j] = src[j * kTT + t];
 #pragma unroll
-                    for (int j = 0; j < C::kWBytes / 16 / 256; ++j) {
+                    for (int j = 0; j < C::kWBytes / 16 / kTT; ++j) {
                         v[j].x = corr_word(v[j].x); v[j].y = corr_word(v[j].y); v[j].z = corr_word(v[j].z); v[j].w = corr_word(v[j].w);
                     }
 #pragma unroll
-                    for (int j = 0; j < C::kWBytes / 16 / 256; ++j) dst[j * 256 + t] = v[j];
+                    for (int j = 0; j < C::kWBytes / 16 / kTT; ++j) dst[j * kTT + t] = v[j];
                     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                     __syncwarp();
                     if (lane == 0) {
@@ -403,6 +401,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
                 }
             };
             uint4 cur[C::kSfRegs], nxt[C::kSfRegs];
+            if (p.pdl) asm volatile("griddepcontrol.wait;" ::: "memory");     // the activation scales come from the kernel in front
             if (first_unit < total_units) load_sf(first_unit, 0, cur);
             uint32_t it = 0;
             bool ok = true;
@@ -440,9 +439,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
         // Eight warps: lane quarter q = warp % 4 (the quarter a warp may read), column half h.  The tensor-memory load
         // of the next 32-column block is in flight while the current one is converted, transposed through shared memory
         // (so that 32 consecutive n of a row go out as 16-byte stores) and stored.
-        const int e = warp < 10 ? warp - 6 : warp - 15;       // 0..7
+        const int e = warp < 10 ? warp - 6 : 4 + warp - kEpi2Warp;       // 0..kEpiWarps-1
         const int q = warp & 3;
-        const int h = warp < 10 ? 0 : 1;
+        const int h = e >> 2;                                            // column group
         __nv_bfloat16* t16 = reinterpret_cast<__nv_bfloat16*>(epi_ptr + e * 2048);
         const bool has_bias = p.bias != nullptr;
         const bool vec_ok = (p.ldo % 8 == 0) && (((uintptr_t)p.out) % 16 == 0);
@@ -459,10 +458,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
             const int n = n0 + lane;
             const float bias = (has_bias && n < p.N) ? __bfloat162float(p.bias[n]) : 0.0f;
             const bool vec = vec_ok && (n0 + 32 <= p.N);
-            const int mbeg = w.m_tile * BN + h * (BN / 2);                  // first activation row of this warp's columns
+            const int mbeg = w.m_tile * BN + h * C::kEpiCols;               // first activation row of this warp's columns
             const int rows_left = p.M - mbeg;
-            const int nchunk = rows_left <= 0 ? 0 : (rows_left >= BN / 2 ? BN / 64 : (rows_left + 31) / 32);
-            const uint32_t taddr0 = tmem + buf * C::kAccStride + ((uint32_t)(q * 32) << 16) + h * (BN / 2);
+            const int nchunk = rows_left <= 0 ? 0 : (rows_left >= C::kEpiCols ? C::kEpiCols / 32 : (rows_left + 31) / 32);
+            const uint32_t taddr0 = tmem + buf * C::kAccStride + ((uint32_t)(q * 32) << 16) + h * C::kEpiCols;
             auto release = [&]() {                                           // every load of this warp has completed
                 tc_fence_before();
                 __syncwarp();
@@ -473,7 +472,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
             };
             // Phase 1: the warp's BN/2 columns leave tensor memory 16 at a time and stay in registers as bf16 pairs
             // (m, m+1); the accumulator is handed back as soon as the last load has completed.
-            constexpr int kBlocks = BN / 64;                       // 32-column blocks per warp
+            constexpr int kBlocks = C::kEpiCols / 32;              // 32-column blocks per warp
             uint32_t pk[kBlocks * 16];
 #pragma unroll
             for (int c = 0; c < kBlocks * 2; ++c) {
@@ -591,8 +590,18 @@ int launch_pair(const CUtensorMap& mw, const CUtensorMap& mx, const CUtensorMap&
     p.m_tiles = (p.M + BN - 1) / BN;
     const int64_t units = (int64_t)((p.n_tiles + 1) / 2) * p.m_tiles;
     const int pairs = (int)(units < clusters[dev] ? units : clusters[dev]);
-    gemm_mxf4_pair_kernel<BN><<<2 * pairs, kPairThreads, C::kSmemBytes, st>>>(mw, mx, mo, p);
-    MXFP4_CHECK_LAUNCH("mxfp4_gemm (tcgen05 cta_group::2 kernel)");
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)(2 * pairs), 1, 1);
+    cfg.blockDim = dim3(kPairThreads, 1, 1);
+    cfg.dynamicSmemBytes = C::kSmemBytes;
+    cfg.stream = st;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr.val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = p.pdl ? 1 : 0;           // may start its set-up while the activation quantiser in front is still running
+    cudaError_t le = cudaLaunchKernelEx(&cfg, gemm_mxf4_pair_kernel<BN>, mw, mx, mo, p);
+    if (le != cudaSuccess) return cuda_fail(le, "mxfp4_gemm (tcgen05 cta_group::2 kernel)");
     return MXFP4_OK;
 }
 

@@ -63,6 +63,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
     // try_wait suspends the thread in hardware until the phase completes or a short time limit passes, so a plain
     // retry loop wakes up with the lowest latency; the abort flag and the bound are looked at every 64 retries.
+    // (An explicit, longer suspend-time hint cut the polling instructions but cost 1 % on large problems.)
     const long long t0 = clock64();
     for (uint32_t it = 1;; ++it) {
         if (mbar_try_wait(bar, parity)) return true;

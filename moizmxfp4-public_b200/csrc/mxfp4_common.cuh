@@ -26,6 +26,31 @@ inline int cuda_fail(cudaError_t e, const char* what) {
 
 int num_sms();  // SM count of the current device (cached per device)
 
+// Launch with programmatic stream serialisation: the grid may be scheduled while the kernel in front of it on the
+// stream is still draining.  Kernels launched this way execute griddepcontrol.wait in every thread before they touch
+// global memory, so results are those of a plain launch; what overlaps is only the scheduling of their CTAs with the
+// tail of the kernel in front (a few microseconds per launch, which is a third of a 4096 x 4096 quantise).
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_chained(void (*kernel)(KArgs...), unsigned grid, unsigned block, cudaStream_t st, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid, 1, 1);
+    cfg.blockDim = dim3(block, 1, 1);
+    cfg.stream = st;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr.val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+// first statements of a kernel launched with launch_chained: let the next launch be scheduled, then wait for the
+// kernel in front (both are no-ops when there is nothing to chain to)
+#define MXFP4_CHAIN_PROLOGUE()                                              \
+    do {                                                                    \
+        asm volatile("griddepcontrol.launch_dependents;" ::: "memory");     \
+        asm volatile("griddepcontrol.wait;" ::: "memory");                  \
+    } while (0)
+
 // ---------------------------------------------------------------------------------------------
 // The reference codebook (quantizer.py:28-33): magnitudes {0.5,.75,1,1.5,2,3,4,6} for codes 0..7,
 // i.e. (1 + m/2) * 2^(e-1) with e = code>>1, m = code&1 -- no zero, unlike hardware E2M1.

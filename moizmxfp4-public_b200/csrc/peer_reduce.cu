@@ -14,7 +14,7 @@
 //   4. publishes done = n and waits until every peer's done >= n: only then may the next GEMM at this call site
 //      overwrite this rank's partial.
 // Every wait is bounded (about ten seconds of clock64: ranks of a job may be seconds apart, a lost rank must not hang the
-// others); a wait that runs out sets the status word and the launch finishes.
+// others); a wait that runs out sets the status word, the launch writes NaN instead of a sum and finishes.
 #include <cstdlib>
 
 #include "mxfp4_common.cuh"
@@ -119,8 +119,17 @@ __global__ void __launch_bounds__(256) peer_allreduce_kernel(const PeerParams p)
                 *reinterpret_cast<uint4*>(p.out + off_out[u]) = make_uint4(o[0], o[1], o[2], o[3]);
             }
         }
-    } else if (threadIdx.x == 0 && p.status) {
-        atomicExch(p.status, MXFP4_E_TIMEOUT);
+    } else {
+        // a peer did not show up: no sum exists.  The output becomes NaN, so that nothing downstream mistakes stale
+        // memory for activations, and the status word says why.
+        if (threadIdx.x == 0 && p.status) atomicExch(p.status, MXFP4_E_TIMEOUT);
+        const int64_t vec_per_row = p.N / 8;
+        const int64_t total = p.M * vec_per_row;
+        const uint4 nan4 = make_uint4(0x7FC07FC0u, 0x7FC07FC0u, 0x7FC07FC0u, 0x7FC07FC0u);
+        for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+            const int64_t m = i / vec_per_row, c = (i - m * vec_per_row) * 8;
+            *reinterpret_cast<uint4*>(p.out + m * p.ldo + c) = nan4;
+        }
     }
     // the last block to get here tells the peers that this rank has finished reading, waits for theirs and closes the call
     __syncthreads();

@@ -18,8 +18,8 @@ from . import _capi
 _MODES = {"exact": _capi.GEMM_EXACT, "fast": _capi.GEMM_FAST}
 _mode = _MODES[os.environ.get("MXFP4_GEMM_MODE", "exact")]
 _lock = threading.RLock()
-_prepared = OrderedDict()        # id(scale tensor) -> (weakref, version, (N, K, ptr), prepared scale tensor)
 _PREPARED_MAX = 4096
+_derived = OrderedDict()         # (id(tensor), tag) -> (weakref, version, ptr, derived tensor, event, ids of streams ordered behind it)
 _workspaces = {}                 # (device index, stream) -> uint8 tensor
 _last_act = {}                   # (device index, stream) -> (activation pointer, M, K, workspace pointer) of the last quantisation
 
@@ -39,39 +39,115 @@ def get_gemm_mode() -> str:
     return "exact" if _mode == _capi.GEMM_EXACT else "fast"
 
 
-def prepared_scales(weight_scales: torch.Tensor, N: int, K: int) -> torch.Tensor:
-    """Tensor-core layout of a weight's E8M0 scales.
-
-    Cached per live tensor OBJECT (a weak reference guards against a recycled address) and per version
-    counter (an in-place update such as load_state_dict invalidates the entry).  A module's buffer hits
-    the cache on every forward; a temporary tensor simply pays one small re-tiling kernel."""
-    key = id(weight_scales)
+def _cached(src: torch.Tensor, tag, build):
+    """Per live tensor OBJECT (a weak reference guards against a recycled address) and version counter (an in-place
+    update such as load_state_dict invalidates the entry): the tensor `build()` derives from `src`, made once, on the
+    stream that was current at first use.  The first reader on any other stream waits for that work through an event
+    (and tells the caching allocator about the new user); after that the stream's own order covers it.  A stream under
+    CUDA graph capture cannot wait for an event recorded outside the capture, so run a layer once on the capturing
+    stream before capturing it (any warm-up call does)."""
+    key = (id(src), tag)
+    dev = src.device
     with _lock:
-        hit = _prepared.get(key)
+        hit = _derived.get(key)
         if hit is not None:
-            ref, version, shape, prepared = hit
-            if ref() is weight_scales and version == weight_scales._version and shape == (N, K, weight_scales.data_ptr()):
-                _prepared.move_to_end(key)
-                return prepared
-            del _prepared[key]
-    L = _capi.load()
-    ws = weight_scales.contiguous()
-    out = torch.empty(L.mxfp4_prepared_scales_bytes(N, K), dtype=torch.uint8, device=ws.device)
-    with _capi.on_device(ws.device):
-        _capi.check(L.mxfp4_prepare_weight_scales(ws.data_ptr(), N, K, out.data_ptr(), _capi.stream_ptr(ws.device)),
-                    "mxfp4_prepare_weight_scales")
+            ref, version, ptr, out, ev, synced = hit
+            if ref() is src and version == src._version and ptr == src.data_ptr():
+                _derived.move_to_end(key)
+                cur = torch.cuda.current_stream(dev)
+                if cur.cuda_stream not in synced:
+                    if torch.cuda.is_current_stream_capturing():
+                        raise _capi.MXFP4BackendError(
+                            "mxfp4: a prepared weight tensor is first used on this stream inside a CUDA graph capture; "
+                            "call the layer once on the capturing stream before the capture")
+                    cur.wait_event(ev)
+                    out.record_stream(cur)
+                    synced.add(cur.cuda_stream)
+                return out
+            del _derived[key]
+    out = build()
+    ev = torch.cuda.Event()
+    cur = torch.cuda.current_stream(dev)
+    ev.record(cur)
 
     def _drop(_ref, key=key):
         with _lock:
-            ent = _prepared.get(key)
+            ent = _derived.get(key)
             if ent is not None and ent[0] is _ref:
-                del _prepared[key]
+                del _derived[key]
 
     with _lock:
-        _prepared[key] = (weakref.ref(weight_scales, _drop), weight_scales._version, (N, K, weight_scales.data_ptr()), out)
-        while len(_prepared) > _PREPARED_MAX:
-            _prepared.popitem(last=False)
+        _derived[key] = (weakref.ref(src, _drop), src._version, src.data_ptr(), out, ev, {cur.cuda_stream})
+        while len(_derived) > _PREPARED_MAX:
+            _derived.popitem(last=False)
     return out
+
+
+def bias_bf16(bias: Optional[torch.Tensor], device) -> Optional[torch.Tensor]:
+    """The bias as a contiguous bf16 tensor on `device`: the tensor itself when it already is one, else a copy made
+    once per parameter version (MXLinear's default bias is float32; casting it on every call cost a launch)."""
+    if bias is None:
+        return None
+    if bias.dtype == torch.bfloat16 and bias.device == device and bias.is_contiguous():
+        return bias
+    if bias.device != device:
+        return bias.detach().to(device=device, dtype=torch.bfloat16).contiguous()
+    return _cached(bias, "bias_bf16", lambda: bias.detach().to(torch.bfloat16).contiguous())
+
+
+def scale_block_size(weight_scales: torch.Tensor, N: int, K: int) -> int:
+    """Block size a scale tensor implies for a packed weight [N, K/2]; raises on anything but [N, K/16|32|64].
+
+    A mis-shaped scale tensor would otherwise be read past its end (or mis-indexed) by the re-tiling kernel."""
+    if weight_scales.dim() != 2 or weight_scales.shape[0] != N or weight_scales.shape[1] == 0 or K % weight_scales.shape[1]:
+        raise _capi.MXFP4BackendError(
+            f"mxfp4: weight_scales of shape {tuple(weight_scales.shape)} do not match a packed weight [{N}, {K // 2}] "
+            f"(expected [{N}, {K}/block] with block 16, 32 or 64)")
+    block = K // weight_scales.shape[1]
+    if block not in (16, 32, 64):
+        raise _capi.MXFP4BackendError(
+            f"mxfp4: weight_scales of shape {tuple(weight_scales.shape)} imply block size {block}; the tensor-core path "
+            "takes 16, 32 or 64 (MXFP4_E_UNSUPPORTED)")
+    return block
+
+
+def prepared_scales(weight_scales: torch.Tensor, N: int, K: int) -> torch.Tensor:
+    """Tensor-core layout of a weight's E8M0 scales [N, K/32] (or [N, K/64]: the tensor cores scale per 32 elements, so
+    every byte of a 64-element block is simply used for both of its halves).
+
+    Cached per live tensor object and version; a module's buffer hits the cache on every forward, a temporary tensor
+    simply pays one small re-tiling kernel."""
+    block = scale_block_size(weight_scales, N, K)
+    if block == 16:
+        raise _capi.MXFP4BackendError("mxfp4: block-16 scales are expanded by expand_block16() before they are prepared")
+
+    def build():
+        L = _capi.load()
+        ws = weight_scales.contiguous()
+        if block == 64:
+            ws = ws.repeat_interleave(2, dim=1).contiguous()
+        out = torch.empty(L.mxfp4_prepared_scales_bytes(N, K), dtype=torch.uint8, device=ws.device)
+        with _capi.on_device(ws.device):
+            _capi.check(L.mxfp4_prepare_weight_scales(ws.data_ptr(), N, K, out.data_ptr(), _capi.stream_ptr(ws.device)),
+                        "mxfp4_prepare_weight_scales")
+        return out
+    return _cached(weight_scales, ("prepared", N, K), build)
+
+
+def expand_block16(packed_weight: torch.Tensor) -> torch.Tensor:
+    """Block-16 weights on 32-element tensor-core blocks: every 16-element block (8 bytes) becomes the first half of a
+    32-element block whose second half is padding, so that the [N, K/16] scales apply unchanged as [N, 2K/32].  The
+    activations are spread the same way with zeros in the padding (spread_block16), which removes the padded weight
+    codes from every dot product.  Costs twice the K extent; block 16 is a side path.  Cached per weight."""
+    def build():
+        N, kb = packed_weight.shape
+        return torch.nn.functional.pad(packed_weight.reshape(N, kb // 8, 8), (0, 8)).reshape(N, kb * 2).contiguous()
+    return _cached(packed_weight, "block16", build)
+
+
+def spread_block16(x: torch.Tensor) -> torch.Tensor:
+    M, K = x.shape
+    return torch.nn.functional.pad(x.reshape(M, K // 16, 16), (0, 16)).reshape(M, 2 * K)
 
 
 def _workspace(device: torch.device, nbytes: int) -> torch.Tensor:
@@ -123,21 +199,24 @@ def quant_matmul_2d(input: torch.Tensor, packed_weight: torch.Tensor, weight_sca
     _capi.require_cuda(packed_weight, "quant_matmul")
     if packed_weight.dtype != torch.uint8:
         raise TypeError("mxfp4: packed_weight must be uint8")
+    block = scale_block_size(weight_scales, N, K)
     if weight_scales.dtype != torch.uint8:
-        return _matmul_bf16_scales(input, packed_weight, weight_scales, bias)
-    if K % 32 != 0:
-        raise _capi.MXFP4BackendError(f"mxfp4: K={K} must be a multiple of 32 (pad activations to the packed weight's width)")
+        return _matmul_bf16_scales(input, packed_weight, weight_scales, bias, block)
     in_dtype = input.dtype
     x = input if in_dtype == torch.bfloat16 else input.to(torch.bfloat16)
+    if block == 16:
+        # twice the K extent: [block of 16 | 16 zeros] against [8 code bytes | 8 padding bytes], scales unchanged
+        y = quant_matmul_2d(spread_block16(x), expand_block16(packed_weight.contiguous()), weight_scales.view(N, -1), bias, out=out)
+        return y if in_dtype == torch.bfloat16 else y.to(in_dtype)
+    if K % 32 != 0:
+        raise _capi.MXFP4BackendError(f"mxfp4: K={K} must be a multiple of 32 (pad activations to the packed weight's width)")
     if x.stride(1) != 1 or (x.stride(0) * 2) % 32 != 0 or x.data_ptr() % 32 != 0:
         x = x.contiguous()
     L = _capi.load()
     dev = x.device
     pw = packed_weight.contiguous()
     sfw = prepared_scales(weight_scales, N, K)
-    b = None
-    if bias is not None:
-        b = bias.to(device=dev, dtype=torch.bfloat16).contiguous()
+    b = bias_bf16(bias, dev)
     if out is None:
         out = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
     if M == 0 or N == 0:
@@ -249,11 +328,11 @@ def quant_matmul_host(input: torch.Tensor, packed_weight: torch.Tensor, weight_s
     return out if in_dtype == torch.bfloat16 else out.to(in_dtype)
 
 
-def _matmul_bf16_scales(input, packed_weight, weight_scales, bias):
+def _matmul_bf16_scales(input, packed_weight, weight_scales, bias, block=32):
     """scale_format="bf16" weights have no power-of-two scales, so they cannot feed the block-scaled
     tensor-core path; they take the reference's own formulation (dequantise, cast, dense matmul,
     src/mxfp4/backends.py:295-312) with this package's dequantiser."""
-    w = _capi.dequantize(packed_weight, weight_scales, 32, torch.float32).to(input.dtype)
+    w = _capi.dequantize(packed_weight, weight_scales, block, torch.float32).to(input.dtype)
     out = torch.matmul(input, w.T)
     if bias is not None:
         out += bias
@@ -269,5 +348,11 @@ def mxlinear_forward(input: torch.Tensor, packed_weight: torch.Tensor, weight_sc
     if x.shape[-1] != k_pad:
         # the quantiser padded the weight rows to a multiple of the block; padded weight columns meet zeros
         x = torch.nn.functional.pad(x, (0, k_pad - x.shape[-1]))
-    y = quant_matmul_2d(x, packed_weight, weight_scales, bias, reuse_act=reuse_act)
+    if bias is not None and x.dtype != torch.bfloat16:
+        # the reference adds the bias in the input's dtype (F.linear, src/mxfp4/modules.py:140); only bf16 inputs get
+        # it from the GEMM epilogue
+        y = quant_matmul_2d(x, packed_weight, weight_scales, None, reuse_act=reuse_act)
+        y = y + bias.to(device=y.device, dtype=y.dtype)
+    else:
+        y = quant_matmul_2d(x, packed_weight, weight_scales, bias, reuse_act=reuse_act)
     return y.reshape(*lead, packed_weight.shape[0])

@@ -28,6 +28,12 @@ from . import _capi
 from . import gemm as _gemm
 from .modules import MXLinear
 
+# The peer-visible buffers come from torch's symmetric memory, whose rendezvous would otherwise also bind them to an
+# NVLink multicast object where the fabric offers one.  The reduction kernel uses plain peer loads and stores only, and
+# a rank that dies while its memory is bound to a multicast object can fault the other ranks' GPUs, so the binding is
+# switched off (torch reads this variable when it first allocates symmetric memory).
+os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+
 
 def _group_info(group):
     if dist.is_available() and dist.is_initialized():
@@ -70,6 +76,7 @@ class _ParallelBase(nn.Module):
 
 class ColumnParallelMXLinear(_ParallelBase):
     """y_shard = x . W[rank rows]^T + b[rank rows]; optionally all-gathers the shards along the last dim."""
+    tp_shard_dim = 0
 
     def __init__(self, in_features, out_features, group=None, gather_output=False):
         super().__init__(in_features, out_features, group)
@@ -133,12 +140,23 @@ class _PeerSum:
         if self.disabled or N % 8:
             return None
         if self.buf is None or M > self.rows or N != self.N:
+            err = None
             try:
                 self._make(M, N, device)
-            except Exception as e:            # no symmetric memory on this system: stay with NCCL
+            except Exception as e:            # no symmetric memory on this system
+                err = e
+            # The choice between the peer kernel and NCCL must be the same on every rank: a rank that fell back alone
+            # would sit in an all-reduce while the others wait for its flags.  Every rank reaches this point together
+            # (same sequence of calls and sizes), so the ranks vote.
+            ok = torch.tensor([0 if err is not None else 1], dtype=torch.int32, device=device)
+            group = self.group if self.group is not None else dist.group.WORLD
+            dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=group)
+            if int(ok.item()) == 0:
                 self.disabled = True
+                self.buf = self.handle = self.blocks = None
                 import warnings
-                warnings.warn(f"mxfp4: peer-memory reduction unavailable ({e}); using the NCCL all-reduce")
+                warnings.warn("mxfp4: peer-memory reduction unavailable on at least one rank"
+                              + (f" (here: {err})" if err is not None else "") + "; all ranks use the NCCL all-reduce")
                 return None
         off = _capi.load().mxfp4_peer_partial_offset()
         return self.buf[off:off + M * N * 2].view(torch.bfloat16).view(M, N)
@@ -146,7 +164,7 @@ class _PeerSum:
     def reduce(self, M, N, bias, world, rank, device):
         L = _capi.load()
         y = torch.empty(M, N, dtype=torch.bfloat16, device=device)
-        b = None if bias is None else bias.to(device=device, dtype=torch.bfloat16).contiguous()
+        b = _gemm.bias_bf16(bias, device)
         with _capi.on_device(device):
             _capi.check(L.mxfp4_peer_allreduce(self.blocks, world, rank, self.epoch.data_ptr(), None if b is None else b.data_ptr(),
                                                y.data_ptr(), N, M, N, N, self.status.data_ptr(), _capi.stream_ptr(device)),
@@ -154,6 +172,9 @@ class _PeerSum:
         return y
 
     def check_status(self):
+        """Synchronises and raises if a launch at this call site gave up waiting for a peer.  Such a launch fills its
+        output with NaN instead of a sum, so the failure also shows in the activations; poll this once per step,
+        outside CUDA graph capture."""
         if self.status is not None and int(self.status.item()) != 0:
             self.status.zero_()
             raise _capi.MXFP4BackendError("mxfp4 peer reduction: a rank did not arrive within the wait bound")
@@ -161,6 +182,7 @@ class _PeerSum:
 
 class RowParallelMXLinear(_ParallelBase):
     """y = all_reduce_sum(x[..., rank slice of K] . W[:, rank slice]^T) + b."""
+    tp_shard_dim = 1
 
     def __init__(self, in_features, out_features, group=None, input_is_parallel=True):
         super().__init__(in_features, out_features, group)
@@ -214,9 +236,11 @@ class MXBlockStack(nn.Module):
         return torch.nn.functional.rms_norm(h, (h.shape[-1],), eps=1e-6)
 
     @classmethod
-    def build(cls, n_layers=32, hidden=4096, inter=11008, device="cuda", group=None, seed=0, block_size=32, fuse=True):
+    def build(cls, n_layers=32, hidden=4096, inter=11008, device="cuda", group=None, seed=0, block_size=32, fuse=True, init="cpu"):
         """Random-init N(0, 0.02) bf16 weights, quantised and sharded for this rank.  Every rank draws the
-        same full matrices from the same CPU generator (seed = layer*7 + j) and keeps its slice.
+        same full matrices from the same generator (seed = layer*7 + j) and keeps its slice: init="cpu" uses torch's
+        CPU generator (the same numbers on every machine: what the parity tests rebuild), init="cuda" the device's
+        (the same numbers on every rank of a job, and seconds instead of minutes for 6.5 G elements).
         fuse=True stores q|k|v and gate|up as one column-parallel layer each (their packed rows concatenated,
         which changes no byte of any of them): one GEMM launch instead of three / two."""
         world, rank = _group_info(group)
@@ -226,12 +250,19 @@ class MXBlockStack(nn.Module):
             for j, (name, n, k, col) in enumerate([("q", hidden, hidden, True), ("k", hidden, hidden, True), ("v", hidden, hidden, True),
                                                    ("o", hidden, hidden, False), ("gate", inter, hidden, True), ("up", inter, hidden, True),
                                                    ("down", hidden, inter, False)]):
-                g = torch.Generator().manual_seed(seed + li * 7 + j)
-                if col:
-                    w = (torch.randn(n, k, generator=g) * 0.02).to(torch.bfloat16)[rank * n // world:(rank + 1) * n // world]
+                if init == "cuda":
+                    g = torch.Generator(device=device).manual_seed(seed + li * 7 + j)
+                    full = (torch.randn(n, k, generator=g, device=device) * 0.02).to(torch.bfloat16)
                 else:
-                    w = (torch.randn(n, k, generator=g) * 0.02).to(torch.bfloat16)[:, rank * k // world:(rank + 1) * k // world]
-                lin = MXLinear.from_linear(_as_linear(w.to(device)), block_size=block_size)
+                    g = torch.Generator().manual_seed(seed + li * 7 + j)
+                    full = (torch.randn(n, k, generator=g) * 0.02).to(torch.bfloat16)
+                if col:
+                    w = full[rank * n // world:(rank + 1) * n // world]
+                else:
+                    w = full[:, rank * k // world:(rank + 1) * k // world]
+                w = w.to(device).contiguous()
+                del full
+                lin = MXLinear.from_linear(_as_linear(w), block_size=block_size)
                 lin.quantize()
                 par = (ColumnParallelMXLinear if col else RowParallelMXLinear)(k, n, group)
                 par._load(lin.packed_weight, lin.weight_scales, None)
@@ -271,10 +302,15 @@ def _as_linear(w: torch.Tensor) -> nn.Linear:
     return lin
 
 
-def parallelize_llama(model: nn.Module, group=None):
+def parallelize_llama(model: nn.Module, group=None, fuse: bool = True):
     """Replace the quantised MXLinear projections of an HF-style Llama (after quantize_model_mxfp4) by
     their tensor-parallel shards: q/k/v/gate/up column-parallel, o/down row-parallel, lm_head
-    column-parallel with gathered logits.  Attention head counts per rank are the caller's business."""
+    column-parallel with gathered logits; with fuse=True the q|k|v and gate|up shards of every block are then
+    stored as one weight each (mxfp4.utils.model_utils.fuse_projections).
+
+    Attention needs no change in models that derive the number of heads from the projection width
+    (`.view(..., -1, head_dim)`, as Hugging Face's LlamaAttention does): every rank then simply attends over
+    heads/world query heads and kv_heads/world key/value heads, which must both be divisible by the world size."""
     col = ("q_proj", "k_proj", "v_proj", "gate_proj", "up_proj")
     row = ("o_proj", "down_proj")
 
@@ -290,4 +326,33 @@ def parallelize_llama(model: nn.Module, group=None):
             else:
                 walk(child)
     walk(model)
+    if fuse:
+        from .utils.model_utils import fuse_projections
+        fuse_projections(model)
     return model
+
+
+def gather_state_dict(model: nn.Module, group=None, dst: Optional[int] = None):
+    """state_dict of a tensor-parallel model in the reference's layout: every sharded packed weight, scale tensor and
+    bias re-assembled from the ranks' shards (column-parallel: rows; row-parallel: columns of K), all other entries as
+    they are.  The result loads into an unsharded quantised model (new.quantize(); new.load_state_dict(sd), the
+    reference's flow in tests/test_modules.py:80-112) and is byte-identical to the state_dict the model had before
+    parallelize_llama.  Collective: every rank must call it; every rank gets the result unless `dst` names one."""
+    world, rank = _group_info(group)
+    sharded = {name: mod.tp_shard_dim for name, mod in model.named_modules() if getattr(mod, "tp_shard_dim", None) is not None}
+    out = {}
+    for key, t in model.state_dict().items():
+        mod_name, _, leaf = key.rpartition(".")
+        if mod_name not in sharded or world == 1:
+            out[key] = t
+            continue
+        dim = sharded[mod_name]
+        if leaf == "bias" and dim == 1:
+            out[key] = t                                   # a row-parallel bias is replicated
+            continue
+        parts = [torch.empty_like(t) for _ in range(world)]
+        dist.all_gather(parts, t.contiguous(), group=group)
+        out[key] = torch.cat(parts, dim=0 if leaf == "bias" else dim)
+    if dst is not None and rank != dst:
+        return None
+    return out

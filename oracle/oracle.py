@@ -129,23 +129,39 @@ def matmul_nt_f64acc(a: torch.Tensor, w: torch.Tensor, bias=None) -> torch.Tenso
     return out
 
 
-def matmul_w4a16(x: torch.Tensor, packed_w: torch.Tensor, w_scales: torch.Tensor, bias=None) -> torch.Tensor:
+def matmul_w4a16(x: torch.Tensor, packed_w: torch.Tensor, w_scales: torch.Tensor, bias=None, block_size: int = 32) -> torch.Tensor:
     """FallbackBackend.matmul (src/mxfp4/backends.py:295-312): dequantise the weight, cast it to the
     input dtype, torch.matmul, add the bias in the output dtype."""
-    wd = dequantize(packed_w, w_scales)
+    wd = dequantize(packed_w, w_scales, block_size)
     out = torch.matmul(x, wd.T.to(x.dtype))
     if bias is not None:
         out += bias
     return out
 
 
-def matmul_operand_matched(x: torch.Tensor, packed_w: torch.Tensor, w_scales: torch.Tensor, bias=None) -> torch.Tensor:
+def act_fake_quantize(x: torch.Tensor, block_size: int = 32) -> torch.Tensor:
+    """bf16 activations as the GEMM sees them: quantised by its own MXFP4 quantiser and decoded again, float32.
+    For block-16 weights the GEMM quantises every 16 elements as a group of their own (padded with zeros to the
+    32 elements the tensor cores scale together); 32- and 64-element weight blocks use 32-element groups."""
+    M, K = x.shape
+    if block_size == 16:
+        xs = torch.nn.functional.pad(x.reshape(M, K // 16, 16), (0, 16)).reshape(M, 2 * K).contiguous()
+        ap, asc = act_quantize(xs)
+        return act_dequantize(ap, asc).reshape(M, K // 16, 32)[:, :, :16].reshape(M, K).contiguous()
+    ap, asc = act_quantize(x)
+    return act_dequantize(ap, asc)
+
+
+def matmul_operand_matched(x: torch.Tensor, packed_w: torch.Tensor, w_scales: torch.Tensor, bias=None, block_size: int = 32,
+                           rows=None) -> torch.Tensor:
     """The gated GEMM oracle: float32 product of the operands the tensor cores actually see --
     activations after the GEMM's own MXFP4 quantiser, weights exactly as the reference dequantises
-    them -- plus the bias, left in float32."""
-    ap, asc = act_quantize(x)
-    a = act_dequantize(ap, asc)
-    wd = dequantize(packed_w, w_scales)
+    them -- plus the bias, left in float32.  `rows` (an index tensor) restricts the product to a sample of the
+    activation rows, for shapes whose full product would take the CPU too long."""
+    a = act_fake_quantize(x.contiguous(), block_size)
+    if rows is not None:
+        a = a[rows]
+    wd = dequantize(packed_w, w_scales, block_size)
     out = torch.matmul(a, wd.T)
     if bias is not None:
         out = out + bias.float()

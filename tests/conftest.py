@@ -88,3 +88,35 @@ def weight(N, K, seed, outliers):
 def act(M, K, seed):
     g = torch.Generator().manual_seed(seed)
     return torch.randn(M, K, generator=g).to(torch.bfloat16)
+
+
+class SmallModel(torch.nn.Module):
+    """Same architecture as the model tests/golden/make_golden.py quantises with the reference."""
+
+    def __init__(self):
+        super().__init__()
+        self.body = torch.nn.Sequential(torch.nn.Linear(64, 128), torch.nn.ReLU(), torch.nn.Linear(128, 96, bias=False))
+        self.head = torch.nn.Linear(96, 10)
+
+    def forward(self, x):
+        return self.head(self.body(x))
+
+
+_DT_OF_KEY = {"packed_weight": "uint8", "weight_scales": "uint8"}
+
+
+def load_model_cases():
+    """model_cases.npz: the reference's quantize_model_mxfp4 / MXLinear.forward on CPU tensors."""
+    z = np.load(os.path.join(GOLDEN, "model_cases.npz"))
+    init = {k[len("model_init_"):]: from_bits(z[k], "float32") for k in z.files if k.startswith("model_init_")}
+    keys = [str(k) for k in z["model_q_keys"]]
+    q = {k: from_bits(z[f"model_q_{k}"], _DT_OF_KEY.get(k.rsplit(".", 1)[-1], "float32")) for k in keys}
+    model = dict(init=init, keys=keys, q=q, x2=from_bits(z["model_x2"], "float32"), y2=from_bits(z["model_y2"], "float32"),
+                 x3=from_bits(z["model_x3"], "float32"), y3=from_bits(z["model_y3"], "float32"))
+    layers = []
+    for i, m in enumerate(z["layer_meta"]):
+        m = json.loads(str(m))
+        layers.append(dict(m, w=from_bits(z[f"l{i}_w"], "float32"), b=from_bits(z[f"l{i}_b"], "float32") if m["bias"] else None,
+                           packed=from_bits(z[f"l{i}_packed"], "uint8"), scales=from_bits(z[f"l{i}_scales"], "uint8"),
+                           x=from_bits(z[f"l{i}_x"], m["dtype"]), y=from_bits(z[f"l{i}_y"], m["dtype"])))
+    return model, layers

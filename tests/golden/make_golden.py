@@ -17,6 +17,9 @@ Files written:
   scale_exhaustive.npz   scale byte for every positive finite bf16 and fp16 value used as block maximum
   from_e8m0.npz          _from_e8m0 for all 256 bytes
   matmul_cases.npz       FallbackBackend.matmul (W4A16 dequantise-then-matmul) on small shapes
+  model_cases.npz        quantize_model_mxfp4 on a small seeded model (state_dict before and after, forward
+                         outputs for 2-D/3-D inputs) and MXLinear.forward for block sizes 16/32/64, ragged
+                         in_features, float32 / float16 / bfloat16 inputs
   fullsize_digests.json  sha256 of inputs and outputs for the full-size benchmark matrices
 """
 import argparse
@@ -92,10 +95,70 @@ def adversarial_blocks_bf16():
     return torch.tensor(rows, dtype=torch.float32).to(torch.bfloat16)
 
 
+class SmallModel(torch.nn.Module):
+    """The model of the reference's tests/test_utils.py:8-20 (fc1, act, fc2, head), one level deeper."""
+
+    def __init__(self):
+        super().__init__()
+        self.body = torch.nn.Sequential(torch.nn.Linear(64, 128), torch.nn.ReLU(), torch.nn.Linear(128, 96, bias=False))
+        self.head = torch.nn.Linear(96, 10)
+
+    def forward(self, x):
+        return self.head(self.body(x))
+
+
+def model_cases(args):
+    """quantize_model_mxfp4 (src/mxfp4/utils/model_utils.py:8-73) and MXLinear.forward (src/mxfp4/modules.py:114-140)
+    as the reference computes them on CPU tensors."""
+    from mxfp4 import MXLinear, quantize_model_mxfp4
+    out, names = {}, []
+    torch.manual_seed(2024)
+    model = SmallModel()
+    for k, v in model.state_dict().items():
+        out[f"model_init_{k}"] = bits(v)
+    x2 = torch.randn(5, 64, generator=torch.Generator().manual_seed(1))
+    x3 = torch.randn(2, 3, 64, generator=torch.Generator().manual_seed(2))
+    quantize_model_mxfp4(model, exclude_layers=["head"], verbose=False)
+    for k, v in model.state_dict().items():
+        out[f"model_q_{k}"] = bits(v)
+    out["model_q_keys"] = np.array(list(model.state_dict().keys()))
+    with torch.no_grad():
+        out["model_x2"], out["model_y2"] = bits(x2), bits(model(x2))
+        out["model_x3"], out["model_y3"] = bits(x3), bits(model(x3))
+    # single layers: (in, out, bias, block, input dtype, leading shape).  in_features is a multiple of the block: the
+    # reference's forward cannot view a padded weight as [out, in] (modules.py:132) for anything else.
+    for i, (fin, fout, bias, block, dt, lead) in enumerate([(128, 64, True, 32, "float32", (8,)), (64, 48, True, 32, "bfloat16", (2, 3)),
+                                                            (256, 32, False, 32, "float16", (4,)), (64, 40, True, 16, "float32", (6,)),
+                                                            (128, 24, True, 64, "bfloat16", (3, 2)), (96, 16, True, 16, "bfloat16", (5,))]):
+        torch.manual_seed(100 + i)
+        layer = MXLinear(fin, fout, bias=bias, block_size=block)
+        w0 = layer.weight.data.clone()
+        tdt = getattr(torch, dt)
+        x = torch.randn(*lead, fin, generator=torch.Generator().manual_seed(200 + i)).to(tdt)
+        layer.quantize()
+        if dt != "float32":
+            layer = layer.to(tdt)          # as model.to(bfloat16) does: the bias follows the activations' dtype
+        with torch.no_grad():
+            y = layer(x)
+        assert y.dtype == tdt
+        names.append(json.dumps(dict(fin=fin, fout=fout, bias=bias, block=block, dtype=dt, lead=list(lead))))
+        out[f"l{i}_w"] = bits(w0)
+        if bias:
+            out[f"l{i}_b"] = bits(layer.bias.data.float())
+        out[f"l{i}_packed"] = bits(layer.packed_weight)
+        out[f"l{i}_scales"] = bits(layer.weight_scales)
+        out[f"l{i}_x"] = bits(x)
+        out[f"l{i}_y"] = bits(y)
+    out["layer_meta"] = np.array(names)
+    np.savez_compressed(os.path.join(HERE, "model_cases.npz"), **out)
+    print(f"model_cases.npz: model + {len(names)} layers")
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", required=True, help="path to a checkout of moizyousufi/MoizMXFP4-public")
     ap.add_argument("--skip-fullsize", action="store_true")
+    ap.add_argument("--only-model", action="store_true", help="write model_cases.npz only")
     args = ap.parse_args()
     sys.path.insert(0, os.path.join(args.reference, "src"))
     from mxfp4.quantizer import MXFP4Quantizer           # noqa: E402
@@ -103,6 +166,9 @@ def main():
 
     torch.set_num_threads(os.cpu_count())
     meta = {"torch": torch.__version__}
+    model_cases(args)
+    if args.only_model:
+        return
 
     # ---------------------------------------------------------------- quantise / dequantise cases
     cases = []

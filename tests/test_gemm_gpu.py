@@ -62,7 +62,11 @@ def test_prepared_weight_scales_layout():
 
 SHAPES = [(1, 128, 32), (33, 128, 32), (17, 100, 96), (32, 128, 256), (64, 128, 512), (128, 256, 1024), (129, 256, 1024),
           (256, 256, 1024), (300, 384, 1376), (384, 256, 512), (576, 384, 1024), (1, 4096, 4096), (16, 4096, 4096), (128, 4096, 4096), (1024, 4096, 4096),
-          (128, 11008, 4096), (128, 4096, 11008), (2048, 1376, 4096)]
+          (128, 11008, 4096), (128, 4096, 11008), (2048, 1376, 4096),
+          # the remaining points of the GEMM sweep (M in {1,16,128,1024,8192} x N in {4096,11008}, K = 4096), the last one
+          # being the benchmark shape; from M = 1024 up a seeded sample of 512 rows is compared
+          (1, 11008, 4096), (16, 11008, 4096), (1024, 11008, 4096), (8192, 4096, 4096), (8192, 11008, 4096)]
+SAMPLE_ROWS = 512
 
 
 @pytest.mark.parametrize("M,N,K", SHAPES)
@@ -76,14 +80,22 @@ def test_gemm_operand_matched_oracle(M, N, K):
     y = quant_matmul(x.cuda(), op.cuda(), os_.cuda(), None if bias is None else bias.cuda())
     gemm.check_status()
     assert y.dtype == torch.bfloat16 and y.shape == (M, N)
-    ref = oracle.matmul_operand_matched(x, op, os_, bias)
-    err = rel_fro(y.float().cpu(), ref)
-    maxabs = (y.float().cpu() - ref).abs().max().item()
-    print(f"M={M} N={N} K={K}: rel_fro={err:.3e} max_abs={maxabs:.4g}")
+    rows = None
+    if M * N > 4 * 1024 * 1024:
+        # large outputs: a seeded sample of rows (always with the first and last row, and rows from every 256-row tile
+        # boundary region) keeps the CPU side to a second or two
+        g = torch.Generator().manual_seed(M + N)
+        rows = torch.cat([torch.tensor([0, M - 1, 255, 256, M - 257]), torch.randperm(M, generator=g)[:SAMPLE_ROWS - 5]]).unique()
+    ycpu = y.float().cpu() if rows is None else y[rows.cuda()].float().cpu()
+    ref = oracle.matmul_operand_matched(x, op, os_, bias, rows=rows)
+    err = rel_fro(ycpu, ref)
+    maxabs = (ycpu - ref).abs().max().item()
+    print(f"M={M} N={N} K={K}: rel_fro={err:.3e} max_abs={maxabs:.4g}" + ("" if rows is None else f" ({rows.numel()} sampled rows)"))
     assert err <= TOL
+    assert bool(torch.isfinite(y.float()).all())
     # against the literal W4A16 reference formulation: bounded by the FP4 activation error
-    lit = oracle.matmul_w4a16(x, op, os_, bias).float()
-    assert rel_fro(y.float().cpu(), lit) < 0.25
+    lit = oracle.matmul_w4a16(x if rows is None else x[rows], op, os_, bias).float()
+    assert rel_fro(ycpu, lit) < 0.25
 
 
 def test_gemm_deterministic_and_fast_mode():
@@ -282,7 +294,7 @@ def test_peer_allreduce_single_gpu_and_bounded_wait(monkeypatch, world):
     """mxfp4_peer_allreduce with all 'ranks' emulated by buffers of one GPU (rank 0 runs; the others are data).  First the
     peers' flags are set by hand, as their launches would set them: the result must be the float32 sum of the partials in
     rank order, rounded once, plus the bias.  Then nothing sets them: the bounded wait runs out, the status word receives
-    MXFP4_E_TIMEOUT and the context stays usable (no fault, no hang)."""
+    MXFP4_E_TIMEOUT, the output is NaN and the context stays usable (no fault, no hang)."""
     import ctypes
     from mxfp4 import _capi
     L = _capi.load()
@@ -324,5 +336,5 @@ def test_peer_allreduce_single_gpu_and_bounded_wait(monkeypatch, world):
     assert rc == 0
     torch.cuda.synchronize()
     assert int(status.item()) == -6                            # MXFP4_E_TIMEOUT
-    assert float(out.float().abs().max()) == 0.0               # nothing was summed
+    assert bool(torch.isnan(out.float()).all())                # no sum exists: the output says so
     assert torch.equal(torch.ones(4, device=dev) * 2, torch.full((4,), 2.0, device=dev))   # the context still works

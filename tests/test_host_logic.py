@@ -110,3 +110,37 @@ def test_dispatcher_without_cuda_raises():
     from mxfp4.backends import get_backend
     with pytest.raises(ValueError):
         get_backend("triton")
+
+
+def test_quantize_model_state_dict_equals_reference_fixture_on_cpu():
+    """Module surgery of quantize_model_mxfp4 with the oracle as the quantiser: keys, dtypes and bytes of the state_dict
+    equal what the reference's own call recorded (tests/golden/model_cases.npz)."""
+    from conftest import SmallModel, load_model_cases
+    from mxfp4 import quantize_model_mxfp4
+    fixture, _ = load_model_cases()
+    model = SmallModel()
+    model.load_state_dict(fixture["init"])
+    quantize_model_mxfp4(model, exclude_layers=["head"], verbose=False)
+    sd = model.state_dict()
+    assert list(sd.keys()) == fixture["keys"]
+    for k in fixture["keys"]:
+        assert sd[k].dtype == fixture["q"][k].dtype and torch.equal(sd[k], fixture["q"][k]), k
+
+
+def test_scale_shape_validation_and_block16_spreading():
+    """Host-side checks in front of the GEMM: a scale tensor must be [N, K/16|32|64]; block-16 operands are spread
+    so that every 16-element block becomes half of a 32-element tensor-core block."""
+    import importlib
+    from mxfp4 import _capi, gemm
+    gemm = importlib.reload(gemm)          # the real functions, not the oracle stand-ins
+    N, K = 8, 128
+    for cols, want in ((8, 16), (4, 32), (2, 64)):
+        assert gemm.scale_block_size(torch.zeros(N, cols, dtype=torch.uint8), N, K) == want
+    for bad in (torch.zeros(N, 3, dtype=torch.uint8), torch.zeros(N - 1, 4, dtype=torch.uint8), torch.zeros(N * 4, dtype=torch.uint8),
+                torch.zeros(N, 1, dtype=torch.uint8), torch.zeros(N, 16, dtype=torch.uint8), torch.zeros(N, 0, dtype=torch.uint8)):
+        with pytest.raises(_capi.MXFP4BackendError):
+            gemm.scale_block_size(bad, N, K)
+    x = torch.arange(2 * 32, dtype=torch.float32).view(2, 32).to(torch.bfloat16)
+    xs = gemm.spread_block16(x)
+    assert xs.shape == (2, 64)
+    assert torch.equal(xs[:, :16], x[:, :16]) and torch.equal(xs[:, 32:48], x[:, 16:]) and float(xs[:, 16:32].abs().max()) == 0

@@ -1,7 +1,8 @@
 """Parity of the CUDA quantiser / dequantiser with the CPU oracle and the reference's golden vectors.
 
 Everything here is bit-exact.  Calls go through the package's public API, which binds the C ABI with
-ctypes; test_capi_gpu.py drives the C entry points directly.
+ctypes (tests/test_capi_symbols.py checks the exported symbols; tests/test_zz_no_alloc.py and tests/test_gemm_gpu.py call
+C entry points directly).
 """
 import hashlib
 import json
@@ -148,3 +149,26 @@ def test_roundtrip_properties_fullsize():
     assert torch.equal(p1, p2)
     neg = q.quantize(-w)[0]
     assert torch.equal(neg ^ 0x88, p1)             # negating the input flips exactly the two sign bits
+
+
+def test_every_positive_bf16_and_fp16_block_maximum_gives_the_reference_scale_byte():
+    """All 32 639 positive finite bf16 values and all 31 743 positive finite fp16 values as a block's maximum: the CUDA
+    quantiser's E8M0 byte equals the byte the reference produced (tests/golden/scale_exhaustive.npz), through the
+    streaming kernel (bf16, contiguous) and the general kernel (fp16; bf16 with a row stride)."""
+    from mxfp4.quantizer import MXFP4Quantizer
+    z = np.load(os.path.join(GOLDEN, "scale_exhaustive.npz"))
+    q = MXFP4Quantizer(32, "e8m0")
+    v = torch.arange(1, 0x7F80, dtype=torch.int32).to(torch.int16).view(torch.bfloat16)
+    blk = torch.zeros(v.numel(), 32, dtype=torch.bfloat16)
+    blk[:, 5] = v
+    _, sc = q.quantize(blk.cuda())
+    assert np.array_equal(sc.cpu().numpy().reshape(-1), z["bf16_scale"])
+    wide = torch.zeros(v.numel(), 64, dtype=torch.bfloat16)
+    wide[:, 5] = v
+    _, sc = q.quantize(wide.cuda()[:, :32])             # strided rows: the general kernel
+    assert np.array_equal(sc.cpu().numpy().reshape(-1), z["bf16_scale"])
+    vh = torch.arange(1, 0x7C00, dtype=torch.int32).to(torch.int16).view(torch.float16)
+    blk = torch.zeros(vh.numel(), 32, dtype=torch.float16)
+    blk[:, 11] = vh
+    _, sc = q.quantize(blk.cuda())
+    assert np.array_equal(sc.cpu().numpy().reshape(-1), z["f16_scale"])
