@@ -148,6 +148,26 @@ MXFP4_API int mxfp4_gemm_prequantized(const uint8_t* a_packed, const uint8_t* a_
                                       int64_t splitk_bytes, int* control_block, void* stream);
 
 /*
+ * mxfp4_gemm_prequantized with two options for chains of kernels (no counterpart in the reference):
+ *   MXFP4_GEMM_CHAINED        the kernel that produced the activations sits directly in front on the stream and signals
+ *                             griddepcontrol.launch_dependents (mxfp4_act_quantize and mxfp4_act_fused do): the GEMM is
+ *                             launched with programmatic stream serialisation, loads weights while that kernel drains and
+ *                             waits for it on the device before it touches the activations;
+ *   MXFP4_GEMM_KEEP_PARTIALS  when the problem is cut along K (mxfp4_gemm_plan says into how many ranges) the float32
+ *                             partial sums stay in splitk_workspace as [ksplit][M][N] and no reduction kernel runs:
+ *                             the consumer sums them (mxfp4_act_fused does); the bias is then NOT applied and out_bf16 is
+ *                             not written.  Without a K-split the flag changes nothing.
+ * mxfp4_gemm_plan: the number of K ranges mxfp4_gemm* uses for a shape (1: no split) and whether CTA pairs run it.
+ */
+#define MXFP4_GEMM_CHAINED 1
+#define MXFP4_GEMM_KEEP_PARTIALS 2
+MXFP4_API int mxfp4_gemm_plan(int64_t M, int64_t N, int64_t K, int mode, int* ksplit, int* cta_pairs);
+MXFP4_API int mxfp4_gemm_prequantized_ex(const uint8_t* a_packed, const uint8_t* a_sf_blocked, const uint8_t* w_packed,
+                                         const uint8_t* w_sf_prepared, const void* bias_bf16, void* out_bf16, int64_t ldo,
+                                         int64_t M, int64_t N, int64_t K, int mode, void* splitk_workspace,
+                                         int64_t splitk_bytes, int* control_block, int flags, void* stream);
+
+/*
  * mxfp4_gemm without any workspace argument and without any device allocation.  It has no counterpart in the
  * reference.  It is for callers that cannot allocate device memory when the matmul is due: a process whose
  * own pool owns the whole GPU and which bans cudaMalloc after start-up, a plugin living inside such a process,
@@ -188,6 +208,53 @@ MXFP4_API int64_t mxfp4_peer_block_bytes(int64_t M, int64_t ld);
 MXFP4_API int64_t mxfp4_peer_partial_offset(void);
 MXFP4_API int mxfp4_peer_allreduce(void* const* blocks, int world, int rank, uint32_t* epoch, const void* bias_bf16, void* out_bf16,
                                    int64_t ldo, int64_t M, int64_t N, int64_t ld, int* status_dev, void* stream);
+
+/*
+ * What lies between two GEMMs of a transformer block, as ONE kernel that ends in the GEMM's activation format.  The
+ * reference has no counterpart: it leaves these steps to the model's PyTorch code (what it does own is the layer on
+ * either side, MXLinear.forward, src/mxfp4/modules.py:114-140).  One launch
+ *   1. gathers the result of the GEMM in front: a bf16 matrix (in_bf16), the float32 partial sums of a K-split
+ *      (in_f32, `splits` of them `split_stride` elements apart; they are summed here in fixed order, so no separate
+ *      reduction kernel runs), or -- tensor parallelism -- the bf16 partial products of all `world` ranks of a
+ *      row-parallel layer in peer-visible blocks laid out as for mxfp4_peer_allreduce (flag handshake included: this
+ *      IS the all-reduce);
+ *   2. applies   MXFP4_ACT_RMSNORM   hidden = residual + (value + bias);  x = hidden * rsqrt(mean(hidden^2) + eps)
+ *                MXFP4_ACT_SILU_MUL  x = silu(value[:, 0:K]) * value[:, K:2K]
+ *                MXFP4_ACT_SUM3      x = value[:, 0:K] + value[:, K:2K] + value[:, 2K:3K]
+ *      rounding to bf16 after every step where the separate PyTorch operations would;
+ *   3. quantises x as mxfp4_act_quantize does: packed [M, K/2] and blocked scales (mxfp4_act_scales_bytes(M, K)).
+ * RMSNORM may also store `hidden` (the new residual stream; may alias `residual`), and with packed == NULL only that.
+ * With all three sources absent RMSNORM takes value = 0 (the first layer of a stack).
+ * peer_wait_done = 0 skips the second handshake ("everybody has finished reading"): allowed when every rank runs
+ * another peer call site between two uses of this one, as the alternating attention / MLP layers of a model do.
+ * Pointers 16-byte aligned, row pitches multiples of 8 elements, K a multiple of 32 and at most 32768.
+ */
+#define MXFP4_ACT_RMSNORM 1
+#define MXFP4_ACT_SILU_MUL 2
+#define MXFP4_ACT_SUM3 3
+typedef struct mxfp4_act_fused_args {
+    int op;
+    const void* in_bf16;       /* device bf16 [M, ld_in] or NULL */
+    const void* in_f32;        /* device float32 [splits][M][ld_in] or NULL */
+    int splits;
+    int64_t split_stride;      /* elements between two partial sums */
+    int64_t ld_in;
+    void* const* peer_blocks;  /* host array [world] of device pointers, or NULL */
+    int world, rank;
+    uint32_t* epoch;           /* device uint32[2], zeroed once (call counter of this call site) */
+    int peer_wait_done;
+    int* status_dev;           /* optional device int: receives MXFP4_E_TIMEOUT; hidden_out is then NaN, codes zero */
+    const void* bias;          /* bf16 [K] or NULL */
+    const void* residual;      /* bf16 [M, ld_res] or NULL */
+    int64_t ld_res;
+    void* hidden_out;          /* bf16 [M, ld_hid] or NULL */
+    int64_t ld_hid;
+    float eps;
+    int64_t M, K;
+    uint8_t* packed;           /* [M, K/2] or NULL */
+    uint8_t* sf;               /* blocked scales */
+} mxfp4_act_fused_args;
+MXFP4_API int mxfp4_act_fused(const mxfp4_act_fused_args* args, void* stream);
 
 #ifdef __cplusplus
 }

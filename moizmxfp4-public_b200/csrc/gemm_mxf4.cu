@@ -646,7 +646,7 @@ constexpr int kControlBytes = 4096;     // control block: int[0] = status word, 
 
 int gemm_run(const uint8_t* a_packed, const uint8_t* a_sf_blocked, const uint8_t* w_packed, const uint8_t* w_sf_prepared,
              const void* bias_bf16, void* out_bf16, int64_t ldo, int64_t M, int64_t N, int64_t K, int mode, void* splitk_workspace,
-             int64_t splitk_bytes, int* status_dev, void* stream, bool behind_act_quantize = false) {
+             int64_t splitk_bytes, int* status_dev, void* stream, bool behind_act_quantize = false, bool keep_partials = false) {
     if (M < 0 || N < 0 || K < 0) { set_error("mxfp4_gemm: negative size"); return MXFP4_E_SHAPE; }
     if (M == 0 || N == 0) return MXFP4_OK;
     if (K == 0 || K % 32) { set_error("mxfp4_gemm: K=%lld must be a positive multiple of 32", (long long)K); return MXFP4_E_SHAPE; }
@@ -675,6 +675,10 @@ int gemm_run(const uint8_t* a_packed, const uint8_t* a_sf_blocked, const uint8_t
     if (want > 1 && splitk_workspace != nullptr && splitk_bytes >= (int64_t)want * M * N * 4 && (uintptr_t)splitk_workspace % 16 == 0) {
         p.ksplit = want;
         p.partial = (float*)splitk_workspace;
+    } else if (want > 1 && keep_partials) {
+        // the caller will read [ksplit][M][N] partial sums as mxfp4_gemm_plan announced them: they must exist
+        set_error("mxfp4_gemm: MXFP4_GEMM_KEEP_PARTIALS needs a 16-byte aligned split-K workspace of %lld bytes", (long long)want * M * N * 4);
+        return MXFP4_E_WORKSPACE;
     }
     p.exact = mode == MXFP4_GEMM_EXACT; p.status = status_dev;
     p.pdl = behind_act_quantize;
@@ -696,7 +700,7 @@ int gemm_run(const uint8_t* a_packed, const uint8_t* a_sf_blocked, const uint8_t
         default: rc = launch_gemm<256>(mw, mx, p, st); break;
     }
     if (rc) return rc;
-    if (p.ksplit > 1) {
+    if (p.ksplit > 1 && !keep_partials) {
         const bool vec = N % 4 == 0 && ldo % 4 == 0 && (uintptr_t)p.out % 8 == 0;
         const int64_t total = vec ? M * N / 4 : M * N;
         int64_t grid = (total + 255) / 256;
@@ -728,6 +732,22 @@ extern "C" int mxfp4_gemm_prequantized(const uint8_t* a_packed, const uint8_t* a
                                        void* stream) {
     return mxfp4::gemm_run(a_packed, a_sf_blocked, w_packed, w_sf_prepared, bias_bf16, out_bf16, ldo, M, N, K, mode, splitk_workspace,
                            splitk_bytes, control_block, stream);
+}
+
+extern "C" int mxfp4_gemm_plan(int64_t M, int64_t N, int64_t K, int mode, int* ksplit, int* cta_pairs) {
+    if (M <= 0 || N <= 0 || K <= 0 || K % 32) { mxfp4::set_error("mxfp4_gemm_plan: bad shape"); return MXFP4_E_SHAPE; }
+    const int pair_bn = mxfp4::pick_pair_bn(M, N, mode == MXFP4_GEMM_EXACT);
+    if (ksplit) *ksplit = pair_bn ? 1 : mxfp4::pick_ksplit(M, N, K);
+    if (cta_pairs) *cta_pairs = pair_bn ? 1 : 0;
+    return MXFP4_OK;
+}
+
+extern "C" int mxfp4_gemm_prequantized_ex(const uint8_t* a_packed, const uint8_t* a_sf_blocked, const uint8_t* w_packed,
+                                          const uint8_t* w_sf_prepared, const void* bias_bf16, void* out_bf16, int64_t ldo, int64_t M,
+                                          int64_t N, int64_t K, int mode, void* splitk_workspace, int64_t splitk_bytes, int* control_block,
+                                          int flags, void* stream) {
+    return mxfp4::gemm_run(a_packed, a_sf_blocked, w_packed, w_sf_prepared, bias_bf16, out_bf16, ldo, M, N, K, mode, splitk_workspace,
+                           splitk_bytes, control_block, stream, (flags & MXFP4_GEMM_CHAINED) != 0, (flags & MXFP4_GEMM_KEEP_PARTIALS) != 0);
 }
 
 extern "C" int mxfp4_gemm(const void* x_bf16, int64_t ldx, const uint8_t* w_packed, const uint8_t* w_sf_prepared, const void* bias_bf16,

@@ -16,6 +16,18 @@ _lib = None
 DT = {torch.bfloat16: 0, torch.float16: 1, torch.float32: 2}
 SF = {"e8m0": 0, "bf16": 1}
 GEMM_EXACT, GEMM_FAST = 0, 1
+GEMM_CHAINED, GEMM_KEEP_PARTIALS = 1, 2
+ACT_RMSNORM, ACT_SILU_MUL, ACT_SUM3 = 1, 2, 3
+
+
+class ActFusedArgs(ctypes.Structure):
+    """struct mxfp4_act_fused_args of include/mxfp4_b200.h"""
+    _fields_ = [("op", ctypes.c_int), ("in_bf16", ctypes.c_void_p), ("in_f32", ctypes.c_void_p), ("splits", ctypes.c_int),
+                ("split_stride", ctypes.c_int64), ("ld_in", ctypes.c_int64), ("peer_blocks", ctypes.POINTER(ctypes.c_void_p)),
+                ("world", ctypes.c_int), ("rank", ctypes.c_int), ("epoch", ctypes.c_void_p), ("peer_wait_done", ctypes.c_int),
+                ("status_dev", ctypes.c_void_p), ("bias", ctypes.c_void_p), ("residual", ctypes.c_void_p), ("ld_res", ctypes.c_int64),
+                ("hidden_out", ctypes.c_void_p), ("ld_hid", ctypes.c_int64), ("eps", ctypes.c_float), ("M", ctypes.c_int64),
+                ("K", ctypes.c_int64), ("packed", ctypes.c_void_p), ("sf", ctypes.c_void_p)]
 
 
 class MXFP4BackendError(RuntimeError):
@@ -63,6 +75,12 @@ def load():
     L.mxfp4_gemm_splitk_bytes.argtypes = [i64, i64, i64]
     L.mxfp4_gemm_splitk_bytes.restype = i64
     L.mxfp4_gemm_prequantized.restype = ci
+    L.mxfp4_gemm_prequantized_ex.argtypes = [vp, vp, vp, vp, vp, vp, i64, i64, i64, i64, ci, vp, i64, vp, ci, vp]
+    L.mxfp4_gemm_prequantized_ex.restype = ci
+    L.mxfp4_gemm_plan.argtypes = [i64, i64, i64, ci, ctypes.POINTER(ci), ctypes.POINTER(ci)]
+    L.mxfp4_gemm_plan.restype = ci
+    L.mxfp4_act_fused.argtypes = [ctypes.POINTER(ActFusedArgs), vp]
+    L.mxfp4_act_fused.restype = ci
     L.mxfp4_peer_block_bytes.argtypes = [i64, i64]
     L.mxfp4_peer_block_bytes.restype = i64
     L.mxfp4_peer_partial_offset.argtypes = []

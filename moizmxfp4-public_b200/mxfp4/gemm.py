@@ -5,6 +5,7 @@ module only keeps, per weight, the scale bytes re-tiled for the tensor cores (a 
 demand, never part of a checkpoint) and, per device and stream, a workspace for the quantised
 activations.
 """
+import ctypes
 import os
 import threading
 import weakref
@@ -326,6 +327,98 @@ def quant_matmul_host(input: torch.Tensor, packed_weight: torch.Tensor, weight_s
             sl["used"] = True
         cur.wait_stream(pipe.s_out)
     return out if in_dtype == torch.bfloat16 else out.to(in_dtype)
+
+
+class FusedChain:
+    """Workspace and launches of a chain  fused activation step -> GEMM -> fused activation step -> ...  on one device
+    and stream (mxfp4_act_fused + mxfp4_gemm_prequantized_ex): the activations between two GEMMs exist only in MXFP4
+    form, a K-split's partial sums are summed by the step that consumes them, and every launch is chained to the one
+    in front.  Buffers grow on demand, so run a chain once eagerly before capturing it in a CUDA graph."""
+
+    def __init__(self, device):
+        self.dev = device
+        self.L = _capi.load()
+        self.ctrl = torch.zeros(1024, dtype=torch.int32, device=device)      # 4 KB control block: status word
+        self.a_packed = self.a_sf = self.out = None
+        self.src = None                                                       # what the last GEMM left for the next step
+
+    def _grow(self, name, nbytes):
+        t = getattr(self, name)
+        if t is None or t.numel() < nbytes:
+            if torch.cuda.is_current_stream_capturing():
+                raise _capi.MXFP4BackendError("mxfp4: run the chain once before capturing it (its buffers are allocated on first use)")
+            setattr(self, name, torch.empty(_align(nbytes, 256), dtype=torch.uint8, device=self.dev))
+        return getattr(self, name)
+
+    def act(self, op, M, K, *, residual=None, hidden_out=None, bias=None, eps=1e-6, peer=None, quantize=True):
+        """One mxfp4_act_fused launch on what the previous gemm() left (or on nothing: the first step of a stack)."""
+        a = _capi.ActFusedArgs()
+        a.op, a.M, a.K, a.eps = op, M, K, eps
+        keep = []
+        if peer is not None:
+            a.peer_blocks, a.world, a.rank = ctypes.cast(peer.blocks, ctypes.POINTER(ctypes.c_void_p)), peer.world, peer.rank
+            a.epoch, a.status_dev, a.peer_wait_done = peer.epoch.data_ptr(), peer.status.data_ptr(), 0 if peer.interleaved else 1
+            a.ld_in = peer.N
+        elif self.src is not None:
+            kind = self.src[0]
+            if kind == "bf16":
+                a.in_bf16, a.ld_in = self.src[1].data_ptr(), self.src[2]
+            else:
+                _, t, splits, stride, ld = self.src
+                a.in_f32, a.splits, a.split_stride, a.ld_in = t.data_ptr(), splits, stride, ld
+            a.status_dev = self.ctrl.data_ptr()
+        if residual is not None:
+            a.residual, a.ld_res = residual.data_ptr(), residual.stride(0)
+        if hidden_out is not None:
+            a.hidden_out, a.ld_hid = hidden_out.data_ptr(), hidden_out.stride(0)
+        if bias is not None:
+            b = bias_bf16(bias, self.dev)
+            keep.append(b)
+            a.bias = b.data_ptr()
+        if quantize:
+            pk = self._grow("a_packed", M * (K // 2))
+            sf = self._grow("a_sf", self.L.mxfp4_act_scales_bytes(M, K))
+            a.packed, a.sf = pk.data_ptr(), sf.data_ptr()
+        with _capi.on_device(self.dev):
+            _capi.check(self.L.mxfp4_act_fused(ctypes.byref(a), _capi.stream_ptr(self.dev)), "mxfp4_act_fused")
+        self.src = None
+        self.act_shape = (M, K)
+
+    def gemm(self, packed_weight, weight_scales, out=None):
+        """GEMM of the activations the last act() produced with a packed weight [N, K/2].  Without `out` the result
+        stays in the chain's own buffer in whatever form is cheapest (bf16, or the partial sums of a K-split) for the
+        next act(); with `out` (bf16 [M, N], e.g. a peer-visible partial buffer) it is a finished bf16 matrix."""
+        M, K = self.act_shape
+        N = packed_weight.shape[0]
+        assert packed_weight.shape[1] * 2 == K, "activation width does not match the weight"
+        sfw = prepared_scales(weight_scales, N, K)
+        ks, pairs = ctypes.c_int(0), ctypes.c_int(0)
+        _capi.check(self.L.mxfp4_gemm_plan(M, N, K, _mode, ctypes.byref(ks), ctypes.byref(pairs)), "mxfp4_gemm_plan")
+        ksplit = ks.value
+        flags = _capi.GEMM_CHAINED
+        need = max(M * N * 2, ksplit * M * N * 4 if ksplit > 1 else 0)
+        if out is None:
+            buf = self._grow("out", need)
+            dst, ldo = buf.data_ptr(), N
+            flags |= _capi.GEMM_KEEP_PARTIALS
+            split_ptr, split_bytes = (buf.data_ptr(), ksplit * M * N * 4) if ksplit > 1 else (None, 0)
+            self.src = ("f32", buf, ksplit, M * N, N) if ksplit > 1 else ("bf16", buf, N)
+        else:
+            dst, ldo = out.data_ptr(), out.stride(0)
+            buf = self._grow("out", ksplit * M * N * 4) if ksplit > 1 else None
+            split_ptr, split_bytes = (buf.data_ptr(), ksplit * M * N * 4) if ksplit > 1 else (None, 0)
+            self.src = ("bf16", out, out.stride(0))
+        with _capi.on_device(self.dev):
+            _capi.check(self.L.mxfp4_gemm_prequantized_ex(self.a_packed.data_ptr(), self.a_sf.data_ptr(), packed_weight.data_ptr(), sfw.data_ptr(),
+                                                          None, dst, ldo, M, N, K, _mode, split_ptr, split_bytes, self.ctrl.data_ptr(), flags,
+                                                          _capi.stream_ptr(self.dev)), "mxfp4_gemm_prequantized_ex")
+        return N
+
+    def check_status(self):
+        code = int(self.ctrl[0].item())
+        if code != 0:
+            self.ctrl[0] = 0
+            raise _capi.MXFP4BackendError(f"mxfp4 fused chain reported status {code} (a device-side wait timed out)")
 
 
 def _matmul_bf16_scales(input, packed_weight, weight_scales, bias, block=32):

@@ -113,6 +113,8 @@ class _PeerSum:
 
     def __init__(self, group):
         self.group = group
+        self.world, self.rank = _group_info(group)
+        self.interleaved = False      # set by a model that runs another peer call site between two uses of this one
         self.rows = 0
         self.N = 0
         self.buf = self.handle = self.blocks = self.epoch = self.status = None
@@ -277,7 +279,16 @@ class MXBlockStack(nn.Module):
             layers.append(nn.ModuleDict(mods))
         return cls(layers)
 
-    def forward(self, h: torch.Tensor) -> torch.Tensor:
+    def forward(self, h: torch.Tensor, fused: Optional[bool] = None) -> torch.Tensor:
+        """fused=True (the default on CUDA for stacks built with fuse=True): every gap between two GEMMs is one
+        mxfp4_act_fused launch (residual add + RMS norm, q+k+v, silu*mul, each ending in the next GEMM's MXFP4 activation
+        format, K-split partial sums and -- under tensor parallelism -- the row-parallel sum over peer memory folded in):
+        eight launches per layer.  fused=False runs the same arithmetic as separate PyTorch operations and layer calls."""
+        if fused is None:
+            fused = h.is_cuda and h.dtype == torch.bfloat16 and h.dim() == 2 and len(self.layers) > 0 and "qkv" in self.layers[0] \
+                and os.environ.get("MXFP4_STACK_FUSED", "1") != "0"
+        if fused:
+            return self._forward_fused(h)
         for L in self.layers:
             x = self._norm(h)
             if "qkv" in L:
@@ -294,6 +305,48 @@ class MXBlockStack(nn.Module):
                 g = torch.nn.functional.silu(L["gate"](x)) * L["up"](x, reuse_act=True)
             h = h + L["down"](g)
         return h
+
+
+def _stack_forward_fused(self, h: torch.Tensor) -> torch.Tensor:
+    dev = h.device
+    chain = getattr(self, "_chain", None)
+    if chain is None or chain.dev != dev:
+        chain = self._chain = _gemm.FusedChain(dev)
+    M, hidden = h.shape
+    hid = h.clone()                                  # the residual stream, updated in place by the RMSNORM steps
+    world = self.layers[0]["o"].world
+    peer_prev = None                                 # peer buffers holding the previous row-parallel layer's partial products
+
+    def row_parallel(layer, peer_ok=True):
+        """GEMM of a row-parallel layer: into the chain's buffer (one rank) or into this rank's peer-visible partial."""
+        if world == 1:
+            chain.gemm(layer.packed_weight, layer.weight_scales)
+            return None
+        if getattr(layer, "_peer", None) is None:
+            layer._peer = _PeerSum(layer.group)
+        layer._peer.interleaved = True               # o and down alternate: a site is never used twice in a row
+        part = layer._peer.partial_view(M, layer.out_features, dev)
+        if part is None:
+            raise _capi.MXFP4BackendError("mxfp4: the fused stack needs the peer-memory reduction (symmetric memory); "
+                                          "call forward(h, fused=False) for the NCCL path")
+        chain.gemm(layer.packed_weight, layer.weight_scales, out=part)
+        return layer._peer
+
+    for L in self.layers:
+        # h = h + (previous down); x = rmsnorm(h)
+        chain.act(_capi.ACT_RMSNORM, M, hidden, residual=hid, hidden_out=hid, peer=peer_prev)
+        n = chain.gemm(L["qkv"].packed_weight, L["qkv"].weight_scales)
+        chain.act(_capi.ACT_SUM3, M, n // 3)                                   # a = q + k + v
+        peer_o = row_parallel(L["o"])
+        chain.act(_capi.ACT_RMSNORM, M, hidden, residual=hid, hidden_out=hid, peer=peer_o)    # h = h + o(a); x = rmsnorm(h)
+        n = chain.gemm(L["gateup"].packed_weight, L["gateup"].weight_scales)
+        chain.act(_capi.ACT_SILU_MUL, M, n // 2)                               # g = silu(gate) * up
+        peer_prev = row_parallel(L["down"])
+    chain.act(_capi.ACT_RMSNORM, M, hidden, residual=hid, hidden_out=hid, peer=peer_prev, quantize=False)   # h = h + down(g)
+    return hid
+
+
+MXBlockStack._forward_fused = _stack_forward_fused
 
 
 def _as_linear(w: torch.Tensor) -> nn.Linear:
