@@ -539,7 +539,9 @@ def extra_tp_stack(rank, world, local, n_layers=32):
     w_elems = n_layers * (4 * 4096 * 4096 + 3 * 11008 * 4096)
     pk = peaks()
     out = {"parallelism": f"tp{world}", "scaling": "strong", "layers": n_layers,
-           "collective": "none" if world == 1 else "64 row-parallel sums of [M, 4096] bf16 per step (mxfp4_peer_allreduce over NVLink peer memory)"}
+           "launches_per_layer": 8,
+           "collective": "none" if world == 1 else "64 row-parallel sums of [M, 4096] bf16 per step over NVLink peer memory, inside mxfp4_act_fused "
+                                                   "(the kernel that also adds the residual, normalises and quantises the next GEMM's activations)"}
     for name, M in (("decode_M128", 128), ("prefill_M2048", 2048)):
         x = torch.randn(M, 4096, generator=torch.Generator().manual_seed(M)).to(torch.bfloat16).to(dev)
         with torch.no_grad():
