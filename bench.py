@@ -714,13 +714,17 @@ def run_decode(args, rank, world, local):
     n_lin = sum(m.weight.numel() for m in model.modules() if isinstance(m, torch.nn.Linear))
     torch.cuda.synchronize()
     t0 = time.time()
-    mxfp4.quantize_model_mxfp4(model, verbose=False)
+    mxfp4.quantize_model_mxfp4(model, verbose=False, fuse=os.environ.get("MXFP4_DECODE_FUSE", "0") != "0")
     torch.cuda.synchronize()
     t_quant = time.time() - t0
+    # Hugging Face's preallocated ("static") KV cache compiles the forward with torch.compile, whose tracing cannot pass
+    # through the C-ABI launches; the default growing cache is used
+    cache = "dynamic"
+    gen_kw = {}
     batch, prompt, new = 128, 512, 128
     ids = torch.randint(0, 32000, (batch, prompt), generator=torch.Generator().manual_seed(4)).to(dev)
     with torch.no_grad():
-        model.generate(ids[:2, :16], max_new_tokens=4, do_sample=False)        # warm-up of kernels and caches
+        model.generate(ids[:2, :16], max_new_tokens=4, do_sample=False, **gen_kw)        # warm-up of kernels and caches
         torch.cuda.synchronize()
         with ClockSampler(local) as cs:
             t0 = time.time()
@@ -728,14 +732,15 @@ def run_decode(args, rank, world, local):
             torch.cuda.synchronize()
             t_prefill = time.time() - t0
             t0 = time.time()
-            out = model.generate(ids, max_new_tokens=new, min_new_tokens=new, do_sample=False)
+            out = model.generate(ids, max_new_tokens=new, min_new_tokens=new, do_sample=False, **gen_kw)
             torch.cuda.synchronize()
             t_gen = time.time() - t0
     gemm.check_status()
     t_dec = max(t_gen - t_prefill, 1e-9)
     return {"metric": "llama7b_shape_decode_tokens_per_s", "value": batch * new / t_dec, "unit": "tokens/s", "ms_per_step": t_dec / new * 1e3,
             "config": {"workload": "random-init Llama-2-7B architecture (HF LlamaForCausalLM), quantize_model_mxfp4 (225 Linear incl. lm_head), "
-                                   "greedy decode of 128 new tokens at batch 128 from 512-token random prompts; HF generate loop and attention",
+                                   "greedy decode of 128 new tokens at batch 128 from 512-token random prompts; "
+                                   f"Hugging Face generate loop and attention, {cache} KV cache",
                        "parallelism": "tp1"},
             "dtype": "fp4 x fp4 linear layers, bf16 elsewhere", "generate_s": t_gen, "prefill_s": t_prefill, "new_tokens": int(out.shape[1] - prompt),
             "quantize_model": {"seconds": t_quant, "linear_elements": n_lin, "gbs": n_lin * QUANT_BYTES_PER_ELEM / t_quant / 1e9},

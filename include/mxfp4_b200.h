@@ -83,6 +83,14 @@ MXFP4_API int mxfp4_quantize(const void* x, int x_dtype, int64_t rows, int64_t c
 MXFP4_API int mxfp4_dequantize(const uint8_t* packed, const void* scales, int scale_fmt, int64_t rows, int64_t cols_pad,
                      int block_size, void* out, int out_dtype, void* stream);
 
+/*
+ * Quantise and dequantise in one pass: out[rows, cols_pad] float32 = dequantize(quantize(x)), bit for bit, without
+ * the packed intermediate.  Replaces the fake-quantisation forward of MXLinear.simulate_quantization,
+ * src/mxfp4/modules.py:144-150 (quantize() + dequantize() of the whole weight per forward).  Arguments as mxfp4_quantize.
+ */
+MXFP4_API int mxfp4_fake_quantize(const void* x, int x_dtype, int64_t rows, int64_t cols, int64_t ld, int block_size,
+                                  int scale_fmt, float* out, void* stream);
+
 /* GEMM modes */
 #define MXFP4_GEMM_EXACT 0 /* weights decode exactly as the reference dequantises them (two MMAs per K step) */
 #define MXFP4_GEMM_FAST 1  /* single pass: weight codes 0 and 1 decode as hardware E2M1 (0, 0.5); NOT parity */

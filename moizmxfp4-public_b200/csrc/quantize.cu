@@ -62,6 +62,32 @@ __global__ void __launch_bounds__(128) quantize_general_kernel(const T* __restri
     }
 }
 
+// Quantise and dequantise in one pass (MXLinear.simulate_quantization, src/mxfp4/modules.py:144-150: the reference runs
+// quantize() and dequantize() back to back on the whole weight in every forward).  Same arithmetic as the two kernels,
+// nothing packed in between: out = +-level[code] * stored_scale, float32, of the padded width.
+template <typename T>
+__global__ void __launch_bounds__(128) fake_quantize_kernel(const T* __restrict__ x, int64_t rows, int64_t cols, int64_t ld, int block,
+                                                            int64_t nblk, int scale_fmt, float* __restrict__ out) {
+    const int64_t total = rows * nblk;
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t r = i / nblk, b = i - r * nblk;
+        const int64_t c0 = b * block;
+        const int64_t left = cols - c0;
+        const int valid = left < block ? (int)left : block;
+        const T* src = x + r * ld + c0;
+        float amax = 0.0f;
+        for (int j = 0; j < valid; ++j) amax = fmaxf(amax, fabsf(to_f32<T>(src[j])));
+        amax = fmaxf(amax, 1e-8f);                             // quantizer.py:90-91
+        const float s = __fdiv_rn(amax, 6.0f);                 // quantizer.py:95-96
+        const float stored = scale_fmt == MXFP4_SF_E8M0 ? e8m0_value(e8m0_byte(s)) : __bfloat162float(__float2bfloat16_rn(s));
+        float* dst = out + r * (nblk * block) + c0;
+        for (int j = 0; j < block; ++j) {
+            const unsigned nib = exact_nibble(j < valid ? to_f32<T>(src[j]) : 0.0f, s);
+            dst[j] = (ref_level(nib & 7u) * ((nib & 8u) ? -1.0f : 1.0f)) * stored;      // quantizer.py:171-193
+        }
+    }
+}
+
 // ------------------------------------------------------------------------------------------------
 // Streaming kernel.
 // ------------------------------------------------------------------------------------------------
@@ -218,4 +244,29 @@ extern "C" int mxfp4_quantize(const void* x, int x_dtype, int64_t rows, int64_t 
         case MXFP4_DT_F16: return launch_general<__half>(x, rows, cols, ld, block_size, scale_fmt, packed, scales, st);
         default: return launch_general<float>(x, rows, cols, ld, block_size, scale_fmt, packed, scales, st);
     }
+}
+
+extern "C" int mxfp4_fake_quantize(const void* x, int x_dtype, int64_t rows, int64_t cols, int64_t ld, int block_size, int scale_fmt,
+                                   float* out, void* stream) {
+    using namespace mxfp4;
+    if (rows < 0 || cols < 0) { set_error("mxfp4_fake_quantize: negative size"); return MXFP4_E_SHAPE; }
+    if (block_size <= 0 || (block_size & 1) || block_size > 1024) { set_error("mxfp4_fake_quantize: block_size %d must be even and in [2, 1024]", block_size); return MXFP4_E_SHAPE; }
+    if (scale_fmt != MXFP4_SF_E8M0 && scale_fmt != MXFP4_SF_BF16) { set_error("mxfp4_fake_quantize: unknown scale format %d", scale_fmt); return MXFP4_E_BADARG; }
+    if (rows == 0 || cols == 0) return MXFP4_OK;
+    if (!x || !out) { set_error("mxfp4_fake_quantize: null pointer"); return MXFP4_E_BADARG; }
+    if (ld < cols) { set_error("mxfp4_fake_quantize: ld < cols"); return MXFP4_E_SHAPE; }
+    const int64_t nblk = (cols + block_size - 1) / block_size;
+    const int64_t total = rows * nblk;
+    int64_t grid = (total + 127) / 128;
+    const int64_t cap = (int64_t)num_sms() * 64;
+    if (grid > cap) grid = cap;
+    cudaStream_t st = (cudaStream_t)stream;
+    switch (x_dtype) {
+        case MXFP4_DT_BF16: fake_quantize_kernel<__nv_bfloat16><<<(unsigned)grid, 128, 0, st>>>((const __nv_bfloat16*)x, rows, cols, ld, block_size, nblk, scale_fmt, out); break;
+        case MXFP4_DT_F16: fake_quantize_kernel<__half><<<(unsigned)grid, 128, 0, st>>>((const __half*)x, rows, cols, ld, block_size, nblk, scale_fmt, out); break;
+        case MXFP4_DT_F32: fake_quantize_kernel<float><<<(unsigned)grid, 128, 0, st>>>((const float*)x, rows, cols, ld, block_size, nblk, scale_fmt, out); break;
+        default: set_error("mxfp4_fake_quantize: unknown dtype %d", x_dtype); return MXFP4_E_BADARG;
+    }
+    MXFP4_CHECK_LAUNCH("mxfp4_fake_quantize");
+    return MXFP4_OK;
 }

@@ -55,7 +55,8 @@ def load():
     L.mxfp4_device_info.argtypes = [ctypes.POINTER(ci)] * 3
     L.mxfp4_quantize.argtypes = [vp, ci, i64, i64, i64, ci, ci, vp, vp, vp]
     L.mxfp4_dequantize.argtypes = [vp, vp, ci, i64, i64, ci, vp, ci, vp]
-    for name in ("mxfp4_device_info", "mxfp4_quantize", "mxfp4_dequantize"):
+    L.mxfp4_fake_quantize.argtypes = [vp, ci, i64, i64, i64, ci, ci, vp, vp]
+    for name in ("mxfp4_device_info", "mxfp4_quantize", "mxfp4_dequantize", "mxfp4_fake_quantize"):
         getattr(L, name).restype = ci
     L.mxfp4_act_scales_bytes.argtypes = [i64, i64]
     L.mxfp4_act_scales_bytes.restype = i64
@@ -184,4 +185,21 @@ def dequantize(packed: torch.Tensor, scales: torch.Tensor, block_size: int, out_
     with on_device(packed.device):
         check(L.mxfp4_dequantize(packed.data_ptr(), scales.data_ptr(), SF[fmt], rows, cols_pad, block_size,
                                  out.data_ptr(), DT[out_dtype], stream_ptr(packed.device)), "mxfp4_dequantize")
+    return out
+
+
+def fake_quantize(x: torch.Tensor, block_size: int, scale_format: str) -> torch.Tensor:
+    """dequantize(quantize(x)) in one kernel: float32 [..., Kpad] (MXLinear.simulate_quantization)."""
+    require_cuda(x, "fake_quantize")
+    L = load()
+    if x.dtype not in DT:
+        x = x.float()
+    x = x.contiguous()
+    cols = x.shape[-1]
+    rows = x.numel() // cols if cols else 0
+    nblk = (cols + block_size - 1) // block_size
+    out = torch.empty(tuple(x.shape[:-1]) + (nblk * block_size,), dtype=torch.float32, device=x.device)
+    with on_device(x.device):
+        check(L.mxfp4_fake_quantize(x.data_ptr(), DT[x.dtype], rows, cols, cols, block_size, SF[scale_format], out.data_ptr(),
+                                    stream_ptr(x.device)), "mxfp4_fake_quantize")
     return out

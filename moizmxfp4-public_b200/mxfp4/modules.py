@@ -89,9 +89,9 @@ class MXLinear(nn.Module):
             from .gemm import mxlinear_forward
             return mxlinear_forward(input, self.packed_weight, self.weight_scales, self.bias, self.in_features)
         if self.simulate_quantization:
-            # fake quantisation: quantise -> dequantise -> dense forward (modules.py:144-150)
-            packed, scales = self.quantizer.quantize(self.weight)
-            w_fake = self.quantizer.dequantize(packed, scales)
+            # fake quantisation: quantise -> dequantise -> dense forward (modules.py:144-150), the first two as one kernel
+            from . import _capi
+            w_fake = _capi.fake_quantize(self.weight.detach(), self.block_size, self.quantizer.scale_format)
             w_fake = w_fake.view(self.out_features, -1)[:, : self.in_features].to(input.dtype)
             return F.linear(input, w_fake, self.bias)
         return F.linear(input, self.weight, self.bias)

@@ -14,6 +14,11 @@ def _dequantize(packed, scales, block_size, out_dtype=torch.float32):
     return oracle.dequantize(packed, scales, block_size).to(out_dtype)
 
 
+def _fake_quantize(x, block_size, scale_format):
+    p, sc = oracle.quantize(x.detach().cpu(), block_size, scale_format)
+    return oracle.dequantize(p, sc, block_size)
+
+
 def _matmul(x, packed, scales, bias=None, out=None, reuse_act=False):
     y = oracle.matmul_operand_matched(x.detach().to(torch.bfloat16), packed, scales, None).to(torch.bfloat16)
     if bias is not None:
@@ -32,7 +37,7 @@ def _forward(x, packed, scales, bias, in_features, reuse_act=False):
 
 def install(monkeypatch=None):
     from mxfp4 import _capi, gemm
-    pairs = [(_capi, "quantize", _quantize), (_capi, "dequantize", _dequantize),
+    pairs = [(_capi, "quantize", _quantize), (_capi, "dequantize", _dequantize), (_capi, "fake_quantize", _fake_quantize),
              (gemm, "quant_matmul_2d", _matmul), (gemm, "mxlinear_forward", _forward)]
     for mod, name, fn in pairs:
         if monkeypatch is not None:

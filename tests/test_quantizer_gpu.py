@@ -172,3 +172,26 @@ def test_every_positive_bf16_and_fp16_block_maximum_gives_the_reference_scale_by
     blk[:, 11] = vh
     _, sc = q.quantize(blk.cuda())
     assert np.array_equal(sc.cpu().numpy().reshape(-1), z["f16_scale"])
+
+
+@pytest.mark.parametrize("case", CASES, ids=[c["name"] for c in CASES])
+def test_fake_quantize_equals_quantize_then_dequantize(case):
+    """mxfp4_fake_quantize (MXLinear.simulate_quantization) against the reference's recorded dequantize(quantize(x))."""
+    from mxfp4 import _capi
+    out = _capi.fake_quantize(case["x"].cuda(), case["block"], case["fmt"])
+    assert out.dtype == torch.float32
+    assert same_bits(out.cpu(), case["rec"]), "fake-quantised values differ from the reference"
+
+
+def test_simulate_quantization_forward():
+    """The QAT-style forward of an unquantised MXLinear: weights fake-quantised, dense forward (modules.py:144-150)."""
+    from mxfp4 import MXLinear
+    torch.manual_seed(3)
+    layer = MXLinear(96, 40, bias=True).cuda()
+    layer.simulate_quantization = True
+    x = torch.randn(5, 96, device="cuda")
+    y = layer(x)
+    p, s = oracle.quantize(layer.weight.detach().cpu())
+    w = oracle.dequantize(p, s)[:, :96]
+    ref = torch.nn.functional.linear(x.cpu(), w, layer.bias.detach().cpu())
+    assert torch.allclose(y.cpu(), ref, rtol=1e-4, atol=1e-5)
