@@ -701,12 +701,18 @@ def run_stack(args, rank, world, local):
 # decode workload: random-init Llama-2-7B architecture, quantize_model_mxfp4, greedy decode (one GPU)
 # ------------------------------------------------------------------------------------------------
 def run_decode(args, rank, world, local):
+    """Config 4: random-init Llama-2-7B architecture (Hugging Face LlamaForCausalLM), quantize_model_mxfp4, greedy decode of
+    128 new tokens at batch 128 from 512-token uniform-random prompts, tensor-parallel over the ranks.  The linear layers
+    run as this library's fused chains (mxfp4.llama.LlamaMXDecoder); attention is torch's scaled_dot_product_attention on
+    a preallocated KV cache; a decode step is replayed from a CUDA graph.  MXFP4_DECODE_HF=1 times Hugging Face's own
+    generate loop on the quantised model instead (one GPU)."""
     import mxfp4
     from mxfp4 import gemm
     from transformers import LlamaConfig, LlamaForCausalLM
     dev = torch.device("cuda", local)
     torch.cuda.set_device(dev)
-    cfg = LlamaConfig(hidden_size=4096, intermediate_size=11008, num_hidden_layers=32, num_attention_heads=32, num_key_value_heads=32,
+    layers = int(os.environ.get("MXFP4_DECODE_LAYERS", "32"))
+    cfg = LlamaConfig(hidden_size=4096, intermediate_size=11008, num_hidden_layers=layers, num_attention_heads=32, num_key_value_heads=32,
                       vocab_size=32000, max_position_embeddings=4096, torch_dtype=torch.bfloat16)
     torch.manual_seed(0)
     with torch.device(dev):
@@ -714,37 +720,72 @@ def run_decode(args, rank, world, local):
     n_lin = sum(m.weight.numel() for m in model.modules() if isinstance(m, torch.nn.Linear))
     torch.cuda.synchronize()
     t0 = time.time()
-    mxfp4.quantize_model_mxfp4(model, verbose=False, fuse=os.environ.get("MXFP4_DECODE_FUSE", "0") != "0")
+    mxfp4.quantize_model_mxfp4(model, verbose=False)
     torch.cuda.synchronize()
     t_quant = time.time() - t0
-    # Hugging Face's preallocated ("static") KV cache compiles the forward with torch.compile, whose tracing cannot pass
-    # through the C-ABI launches; the default growing cache is used
-    cache = "dynamic"
-    gen_kw = {}
     batch, prompt, new = 128, 512, 128
     ids = torch.randint(0, 32000, (batch, prompt), generator=torch.Generator().manual_seed(4)).to(dev)
+    hf = os.environ.get("MXFP4_DECODE_HF", "0") == "1" and world == 1
     with torch.no_grad():
-        model.generate(ids[:2, :16], max_new_tokens=4, do_sample=False, **gen_kw)        # warm-up of kernels and caches
-        torch.cuda.synchronize()
-        with ClockSampler(local) as cs:
-            t0 = time.time()
-            model(ids[:, :prompt])                                              # prefill alone, to separate it from decode
+        if hf:
+            model.generate(ids[:2, :16], max_new_tokens=4, do_sample=False)        # warm-up of kernels and caches
             torch.cuda.synchronize()
+            with ClockSampler(local) as cs:
+                t0 = time.time()
+                model(ids[:, :prompt])                                              # prefill alone, to separate it from decode
+                torch.cuda.synchronize()
+                t_prefill = time.time() - t0
+                t0 = time.time()
+                out = model.generate(ids, max_new_tokens=new, min_new_tokens=new, do_sample=False)
+                torch.cuda.synchronize()
+                t_gen = time.time() - t0
+            t_dec = max(t_gen - t_prefill, 1e-9)
+            n_new = int(out.shape[1] - prompt)
+            how = "Hugging Face generate loop and attention, growing KV cache"
+        else:
+            from mxfp4.llama import LlamaMXDecoder
+            dec = LlamaMXDecoder(model, batch, prompt + new)
+            del model
+            torch.cuda.empty_cache()
+            dec.prefill(ids[:16, :64]); dec.decode(3)                                # warm-up: buffers, peer set-up, graph capture of a small batch
+            barrier(world)
+            t0 = time.time()
+            dec.prefill(ids)
+            torch.cuda.synchronize()
+            barrier(world)
             t_prefill = time.time() - t0
-            t0 = time.time()
-            out = model.generate(ids, max_new_tokens=new, min_new_tokens=new, do_sample=False, **gen_kw)
-            torch.cuda.synchronize()
-            t_gen = time.time() - t0
+            dec.decode(2)                                                            # captures the batch-128 step
+            dec.prefill(ids)
+            barrier(world)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            with ClockSampler(local) as cs:
+                e0.record()
+                toks = dec.decode(new)
+                e1.record()
+                torch.cuda.synchronize()
+            t_dec = max_over_ranks(e0.elapsed_time(e1), world, dev) * 1e-3
+            t_gen = t_dec + t_prefill
+            n_new = int(toks.shape[1])
+            dec.chain.check_status()
+            how = ("fused MXFP4 chains for the linear layers (8 launches + attention per layer), torch scaled_dot_product_attention on a "
+                   "preallocated KV cache, decode step replayed from a CUDA graph")
     gemm.check_status()
-    t_dec = max(t_gen - t_prefill, 1e-9)
-    return {"metric": "llama7b_shape_decode_tokens_per_s", "value": batch * new / t_dec, "unit": "tokens/s", "ms_per_step": t_dec / new * 1e3,
-            "config": {"workload": "random-init Llama-2-7B architecture (HF LlamaForCausalLM), quantize_model_mxfp4 (225 Linear incl. lm_head), "
-                                   "greedy decode of 128 new tokens at batch 128 from 512-token random prompts; "
-                                   f"Hugging Face generate loop and attention, {cache} KV cache",
-                       "parallelism": "tp1"},
-            "dtype": "fp4 x fp4 linear layers, bf16 elsewhere", "generate_s": t_gen, "prefill_s": t_prefill, "new_tokens": int(out.shape[1] - prompt),
+    steps = max(n_new - 1, 1) if not hf else n_new
+    return {"metric": "llama7b_shape_decode_tokens_per_s", "value": batch * steps / t_dec, "unit": "tokens/s", "ms_per_step": t_dec / steps * 1e3,
+            "config": {"workload": f"random-init Llama-2-7B architecture ({layers} layers), quantize_model_mxfp4 (225 Linear incl. lm_head), "
+                                   "greedy decode of 128 new tokens at batch 128 from 512-token random prompts; " + how,
+                       "parallelism": f"tp{world}"},
+            "dtype": "fp4 x fp4 linear layers, bf16 elsewhere", "generate_s": t_gen, "prefill_s": t_prefill, "new_tokens": n_new,
             "quantize_model": {"seconds": t_quant, "linear_elements": n_lin, "gbs": n_lin * QUANT_BYTES_PER_ELEM / t_quant / 1e9},
-            "gpu_launches": None, "clocks": cs.summary()}
+            "gpu_launches": None, "clocks": cs.summary(), "scaling_note": "strong"}
+
+
+def extra_llama_decode(args, rank, world, local):
+    """Config 4 as a sub-record of the default line: Llama-2-7B-shape greedy decode, tensor-parallel over the ranks."""
+    r = run_decode(args, rank, world, local)
+    return {"value": r["value"], "unit": r["unit"], "ms_per_step": r["ms_per_step"], "parallelism": r["config"]["parallelism"], "scaling": "strong",
+            "workload": r["config"]["workload"], "prefill_s": r["prefill_s"], "new_tokens": r["new_tokens"], "quantize_model": r["quantize_model"],
+            "clocks": r["clocks"]}
 
 
 # DRAM traffic of one GEMM launch (dram__bytes_read.sum + dram__bytes_write.sum, one ncu capture; see profiles/)
@@ -805,7 +846,8 @@ def main():
     if args.workload == "gemm" and not args.no_extras and not args.gemm_shape:
         extra = {}
         for name, fn in (("quantize_dequantize", (lambda: extra_quantize_dequantize(local)) if world == 1 else None),
-                         ("tp_stack", lambda: extra_tp_stack(rank, world, local))):
+                         ("tp_stack", lambda: extra_tp_stack(rank, world, local)),
+                         ("llama_decode", lambda: extra_llama_decode(args, rank, world, local))):
             if fn is None:
                 continue
             try:

@@ -226,9 +226,10 @@ MXFP4_API int mxfp4_peer_allreduce(void* const* blocks, int world, int rank, uin
  *      reduction kernel runs), or -- tensor parallelism -- the bf16 partial products of all `world` ranks of a
  *      row-parallel layer in peer-visible blocks laid out as for mxfp4_peer_allreduce (flag handshake included: this
  *      IS the all-reduce);
- *   2. applies   MXFP4_ACT_RMSNORM   hidden = residual + (value + bias);  x = hidden * rsqrt(mean(hidden^2) + eps)
+ *   2. applies   MXFP4_ACT_RMSNORM   hidden = residual + (value + bias);  x = gamma * (hidden * rsqrt(mean(hidden^2) + eps))
  *                MXFP4_ACT_SILU_MUL  x = silu(value[:, 0:K]) * value[:, K:2K]
  *                MXFP4_ACT_SUM3      x = value[:, 0:K] + value[:, K:2K] + value[:, 2K:3K]
+ *                MXFP4_ACT_IDENTITY  x = value
  *      rounding to bf16 after every step where the separate PyTorch operations would;
  *   3. quantises x as mxfp4_act_quantize does: packed [M, K/2] and blocked scales (mxfp4_act_scales_bytes(M, K)).
  * RMSNORM may also store `hidden` (the new residual stream; may alias `residual`), and with packed == NULL only that.
@@ -240,6 +241,7 @@ MXFP4_API int mxfp4_peer_allreduce(void* const* blocks, int world, int rank, uin
 #define MXFP4_ACT_RMSNORM 1
 #define MXFP4_ACT_SILU_MUL 2
 #define MXFP4_ACT_SUM3 3
+#define MXFP4_ACT_IDENTITY 4
 typedef struct mxfp4_act_fused_args {
     int op;
     const void* in_bf16;       /* device bf16 [M, ld_in] or NULL */
@@ -261,6 +263,7 @@ typedef struct mxfp4_act_fused_args {
     int64_t M, K;
     uint8_t* packed;           /* [M, K/2] or NULL */
     uint8_t* sf;               /* blocked scales */
+    const void* gamma;         /* bf16 [K] or NULL: the norm's learned weight (RMSNORM) */
 } mxfp4_act_fused_args;
 MXFP4_API int mxfp4_act_fused(const mxfp4_act_fused_args* args, void* stream);
 

@@ -8,9 +8,10 @@
 //      order, so the separate reduction kernel disappears), or -- tensor parallelism -- the bf16 partial products of
 //      all ranks of a row-parallel layer, read over NVLink peer memory after a flag handshake (the all-reduce);
 //   2. applies the step in between:
-//        RMSNORM   hidden = residual + value (+ bias);  x = hidden * rsqrt(mean(hidden^2) + eps)
+//        RMSNORM   hidden = residual + value (+ bias);  x = hidden * rsqrt(mean(hidden^2) + eps) (* gamma)
 //        SILU_MUL  x = silu(value[:, :K]) * value[:, K:2K]
 //        SUM3      x = value[:, :K] + value[:, K:2K] + value[:, 2K:3K]
+//        IDENTITY  x = value
 //      with the bf16 roundings the unfused PyTorch operations would make after each step;
 //   3. quantises x exactly as mxfp4_act_quantize does and writes packed codes + blocked scales.
 // One CTA per activation row; a thread owns a few 8-element chunks and keeps them in registers between the two passes
@@ -57,6 +58,7 @@ struct FusedParams {
     int wait_done;                    // also wait for the "done" handshake (call sites that are reused back to back)
     int* status;
     const __nv_bfloat16* bias;        // [K] or null, added to the value
+    const __nv_bfloat16* gamma;       // [K] or null (RMSNORM): the norm's learned weight
     const __nv_bfloat16* residual;    // [M, ld_res] or null (RMSNORM)
     int64_t ld_res;
     __nv_bfloat16* hidden_out;        // [M, ld_hid] or null (RMSNORM): residual + value
@@ -210,6 +212,8 @@ __global__ void __launch_bounds__(512) act_fused_kernel(const FusedParams p) {
                         x[i] = bf16_round(sl * u[i]);
                     }
                     xp[it] = pack8(x);
+                } else if (p.op == MXFP4_ACT_IDENTITY) {
+                    xp[it] = pack8(x);
                 } else {   // MXFP4_ACT_SUM3
                     float a[8];
                     load_value8(p, m, p.K + c, a);
@@ -242,9 +246,13 @@ __global__ void __launch_bounds__(512) act_fused_kernel(const FusedParams p) {
                 float amax = 0.0f;
                 if (ci < chunks) {
                     unpack8(xp[it], x);
+                    float gm[8];
+                    const bool scaled = p.op == MXFP4_ACT_RMSNORM && p.gamma != nullptr;
+                    if (scaled) unpack8(__ldg(reinterpret_cast<const uint4*>(p.gamma + ci * 8)), gm);
 #pragma unroll
                     for (int i = 0; i < 8; ++i) {
                         if (p.op == MXFP4_ACT_RMSNORM) x[i] = bf16_round(x[i] * r);
+                        if (scaled) x[i] = bf16_round(gm[i] * x[i]);          // weight * normalised, both bf16
                         amax = fmaxf(amax, fabsf(x[i]));
                     }
                 }
@@ -313,7 +321,7 @@ __global__ void __launch_bounds__(512) act_fused_kernel(const FusedParams p) {
 extern "C" int mxfp4_act_fused(const mxfp4_act_fused_args* a, void* stream) {
     using namespace mxfp4;
     if (!a) { set_error("mxfp4_act_fused: null argument block"); return MXFP4_E_BADARG; }
-    if (a->op != MXFP4_ACT_RMSNORM && a->op != MXFP4_ACT_SILU_MUL && a->op != MXFP4_ACT_SUM3) {
+    if (a->op != MXFP4_ACT_RMSNORM && a->op != MXFP4_ACT_SILU_MUL && a->op != MXFP4_ACT_SUM3 && a->op != MXFP4_ACT_IDENTITY) {
         set_error("mxfp4_act_fused: unknown op %d", a->op);
         return MXFP4_E_BADARG;
     }
@@ -325,21 +333,21 @@ extern "C" int mxfp4_act_fused(const mxfp4_act_fused_args* a, void* stream) {
         return MXFP4_E_UNSUPPORTED;
     }
     if (a->M > 0x7FFFFFFF) { set_error("mxfp4_act_fused: too many rows"); return MXFP4_E_SHAPE; }
-    const int width = a->op == MXFP4_ACT_RMSNORM ? 1 : (a->op == MXFP4_ACT_SILU_MUL ? 2 : 3);
+    const int width = a->op == MXFP4_ACT_SILU_MUL ? 2 : (a->op == MXFP4_ACT_SUM3 ? 3 : 1);
     const int sources = (a->in_bf16 != nullptr) + (a->in_f32 != nullptr) + (a->world > 1);
     if (sources > 1) { set_error("mxfp4_act_fused: give one source (in_bf16, in_f32 partial sums, or peer blocks)"); return MXFP4_E_BADARG; }
     if (sources == 0 && !(a->op == MXFP4_ACT_RMSNORM && a->residual)) { set_error("mxfp4_act_fused: no input"); return MXFP4_E_BADARG; }
     if (sources == 1 && a->ld_in < width * a->K) { set_error("mxfp4_act_fused: ld_in %lld < %d * K", (long long)a->ld_in, width); return MXFP4_E_SHAPE; }
     if (a->in_f32 && (a->splits < 1 || a->splits > 64)) { set_error("mxfp4_act_fused: splits=%d", a->splits); return MXFP4_E_BADARG; }
-    if (a->op != MXFP4_ACT_RMSNORM && (a->residual || a->hidden_out || a->bias || a->world > 1)) {
-        set_error("mxfp4_act_fused: residual, hidden_out, bias and peer input belong to the RMSNORM op");
+    if (a->op != MXFP4_ACT_RMSNORM && (a->residual || a->hidden_out || a->bias || a->gamma || a->world > 1)) {
+        set_error("mxfp4_act_fused: residual, hidden_out, bias, gamma and peer input belong to the RMSNORM op");
         return MXFP4_E_BADARG;
     }
     if (!a->packed && !a->hidden_out) { set_error("mxfp4_act_fused: nothing to produce"); return MXFP4_E_BADARG; }
     if (a->packed && !a->sf) { set_error("mxfp4_act_fused: packed without scale buffer"); return MXFP4_E_BADARG; }
     // 16-byte vector accesses everywhere
     if ((uintptr_t)a->in_bf16 % 16 || (uintptr_t)a->in_f32 % 16 || (uintptr_t)a->residual % 16 || (uintptr_t)a->hidden_out % 16 ||
-        (uintptr_t)a->packed % 16 || (uintptr_t)a->bias % 16 || a->ld_in % 8 || a->ld_res % 8 || a->ld_hid % 8 || a->split_stride % 4) {
+        (uintptr_t)a->packed % 16 || (uintptr_t)a->bias % 16 || (uintptr_t)a->gamma % 16 || a->ld_in % 8 || a->ld_res % 8 || a->ld_hid % 8 || a->split_stride % 4) {
         set_error("mxfp4_act_fused: pointers must be 16-byte aligned and row pitches multiples of 8 elements");
         return MXFP4_E_ALIGN;
     }
@@ -364,7 +372,7 @@ extern "C" int mxfp4_act_fused(const mxfp4_act_fused_args* a, void* stream) {
         p.wait_done = a->peer_wait_done ? 1 : 0;
     }
     p.status = a->status_dev;
-    p.bias = (const __nv_bfloat16*)a->bias; p.residual = (const __nv_bfloat16*)a->residual; p.ld_res = a->ld_res;
+    p.bias = (const __nv_bfloat16*)a->bias; p.gamma = (const __nv_bfloat16*)a->gamma; p.residual = (const __nv_bfloat16*)a->residual; p.ld_res = a->ld_res;
     p.hidden_out = (__nv_bfloat16*)a->hidden_out; p.ld_hid = a->ld_hid;
     p.eps = a->eps; p.M = a->M; p.K = a->K;
     p.packed = a->packed; p.sf = a->sf;

@@ -17,7 +17,7 @@ DT = {torch.bfloat16: 0, torch.float16: 1, torch.float32: 2}
 SF = {"e8m0": 0, "bf16": 1}
 GEMM_EXACT, GEMM_FAST = 0, 1
 GEMM_CHAINED, GEMM_KEEP_PARTIALS = 1, 2
-ACT_RMSNORM, ACT_SILU_MUL, ACT_SUM3 = 1, 2, 3
+ACT_RMSNORM, ACT_SILU_MUL, ACT_SUM3, ACT_IDENTITY = 1, 2, 3, 4
 
 
 class ActFusedArgs(ctypes.Structure):
@@ -27,7 +27,7 @@ class ActFusedArgs(ctypes.Structure):
                 ("world", ctypes.c_int), ("rank", ctypes.c_int), ("epoch", ctypes.c_void_p), ("peer_wait_done", ctypes.c_int),
                 ("status_dev", ctypes.c_void_p), ("bias", ctypes.c_void_p), ("residual", ctypes.c_void_p), ("ld_res", ctypes.c_int64),
                 ("hidden_out", ctypes.c_void_p), ("ld_hid", ctypes.c_int64), ("eps", ctypes.c_float), ("M", ctypes.c_int64),
-                ("K", ctypes.c_int64), ("packed", ctypes.c_void_p), ("sf", ctypes.c_void_p)]
+                ("K", ctypes.c_int64), ("packed", ctypes.c_void_p), ("sf", ctypes.c_void_p), ("gamma", ctypes.c_void_p)]
 
 
 class MXFP4BackendError(RuntimeError):

@@ -350,7 +350,12 @@ class FusedChain:
             setattr(self, name, torch.empty(_align(nbytes, 256), dtype=torch.uint8, device=self.dev))
         return getattr(self, name)
 
-    def act(self, op, M, K, *, residual=None, hidden_out=None, bias=None, eps=1e-6, peer=None, quantize=True):
+    def feed(self, x: torch.Tensor):
+        """Makes a bf16 matrix [M, K] (row pitch = stride(0)) the input of the next act() -- e.g. an attention output."""
+        assert x.dim() == 2 and x.dtype == torch.bfloat16 and x.stride(1) == 1
+        self.src = ("bf16", x, x.stride(0))
+
+    def act(self, op, M, K, *, residual=None, hidden_out=None, bias=None, gamma=None, eps=1e-6, peer=None, quantize=True):
         """One mxfp4_act_fused launch on what the previous gemm() left (or on nothing: the first step of a stack)."""
         a = _capi.ActFusedArgs()
         a.op, a.M, a.K, a.eps = op, M, K, eps
@@ -375,6 +380,10 @@ class FusedChain:
             b = bias_bf16(bias, self.dev)
             keep.append(b)
             a.bias = b.data_ptr()
+        if gamma is not None:
+            g = bias_bf16(gamma, self.dev)
+            keep.append(g)
+            a.gamma = g.data_ptr()
         if quantize:
             pk = self._grow("a_packed", M * (K // 2))
             sf = self._grow("a_sf", self.L.mxfp4_act_scales_bytes(M, K))

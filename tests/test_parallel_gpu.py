@@ -80,7 +80,37 @@ def _worker(rank, world, port, q):
         ref = [torch.empty_like(out) for _ in range(world)]
         dist.all_gather(ref, out)
         same = all(torch.equal(ref[0], r) for r in ref)           # every rank ends with the same replicated activations
-        q.put((rank, ok_col and ok_peer and err < 1e-2 and fin and same, err))
+        # the Llama decoder under tensor parallelism against the same decoder on one rank (a one-rank group per process)
+        from transformers import LlamaConfig, LlamaForCausalLM
+        from mxfp4 import quantize_model_mxfp4
+        from mxfp4.llama import LlamaMXDecoder
+        solo = None
+        for r in range(world):
+            g = dist.new_group([r])
+            if r == rank:
+                solo = g
+        heads = max(4, world)
+        cfg = LlamaConfig(hidden_size=32 * heads, intermediate_size=64 * world, num_hidden_layers=2, num_attention_heads=heads,
+                          num_key_value_heads=heads, vocab_size=32 * world, max_position_embeddings=64, tie_word_embeddings=False)
+        torch.manual_seed(0)
+        model = LlamaForCausalLM(cfg).to(torch.bfloat16).eval().to(dev)
+        quantize_model_mxfp4(model, verbose=False)
+        ids = torch.randint(0, cfg.vocab_size, (5, 7), generator=torch.Generator().manual_seed(2)).to(dev)
+        with torch.no_grad():
+            ref = LlamaMXDecoder(model, 5, 16, group=solo)._forward(ids, 7).float()
+            tp = LlamaMXDecoder(model, 5, 16)
+            part = tp._forward(ids, 7)
+            parts = [torch.empty_like(part) for _ in range(world)]
+            dist.all_gather(parts, part)
+            lg = torch.cat(parts, -1).float()
+            err_dec = ((lg - ref).norm() / ref.norm()).item()
+            tp.prefill(ids)
+            toks = tp.decode(4)
+            tl = [torch.empty_like(toks) for _ in range(world)]
+            dist.all_gather(tl, toks)
+            same_toks = all(torch.equal(tl[0], t) for t in tl)
+            tp.chain.check_status()
+        q.put((rank, ok_col and ok_peer and err < 1e-2 and fin and same and err_dec < 5e-2 and same_toks, (err, err_dec)))
     except Exception as e:                     # report instead of leaving the parent to time out
         q.put((rank, False, repr(e)))
         raise
