@@ -744,25 +744,37 @@ def run_decode(args, rank, world, local):
             how = "Hugging Face generate loop and attention, growing KV cache"
         else:
             from mxfp4.llama import LlamaMXDecoder
+
+            def note(msg):
+                if os.environ.get("MXFP4_BENCH_TRACE"):
+                    sys.stderr.write(f"[rank {rank}] {time.strftime('%H:%M:%S')} decode: {msg}\n"); sys.stderr.flush()
             dec = LlamaMXDecoder(model, batch, prompt + new)
             del model
             torch.cuda.empty_cache()
-            dec.prefill(ids[:16, :64]); dec.decode(3)                                # warm-up: buffers, peer set-up, graph capture of a small batch
             barrier(world)
+            note("first prefill (buffers, peer set-up)")
+            dec.prefill(ids)
+            torch.cuda.synchronize()
+            barrier(world)
+            note("timed prefill")
             t0 = time.time()
             dec.prefill(ids)
             torch.cuda.synchronize()
             barrier(world)
             t_prefill = time.time() - t0
+            note("graph capture")
             dec.decode(2)                                                            # captures the batch-128 step
+            torch.cuda.synchronize()
             dec.prefill(ids)
             barrier(world)
+            note("timed decode")
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             with ClockSampler(local) as cs:
                 e0.record()
                 toks = dec.decode(new)
                 e1.record()
                 torch.cuda.synchronize()
+            note("done")
             t_dec = max_over_ranks(e0.elapsed_time(e1), world, dev) * 1e-3
             t_gen = t_dec + t_prefill
             n_new = int(toks.shape[1])
@@ -852,6 +864,8 @@ def main():
                 continue
             try:
                 torch.cuda.empty_cache()
+                if os.environ.get("MXFP4_BENCH_TRACE"):
+                    sys.stderr.write(f"[rank {rank}] {time.strftime('%H:%M:%S')} extra: {name}\n"); sys.stderr.flush()
                 r = fn()
                 if name == "quantize_dequantize":
                     extra.update(r)

@@ -9,13 +9,13 @@ tensor parallelism run inside those same kernels over peer memory, q|k|v and gat
 (rotary embedding, KV cache, softmax(QK^T)V) is torch's scaled_dot_product_attention on a preallocated cache: it is not part
 of this library.  A decode step has fixed shapes and is replayed from a CUDA graph.
 
-Tensor parallelism: q/k/v/gate/up and the vocabulary projection are split by output rows (whole heads per rank), o and
-down by input columns; every rank holds the KV cache of its own heads.
+Tensor parallelism: q/k/v/gate/up are split by output rows (whole heads per rank), o and down by input columns; every
+rank holds the KV cache of its own heads.  The only exchange is the row-parallel sum, which runs inside mxfp4_act_fused:
+a decode step contains no NCCL call.
 """
 from typing import Optional
 
 import torch
-import torch.distributed as dist
 import torch.nn.functional as F
 
 from . import _capi
@@ -68,9 +68,9 @@ class LlamaMXDecoder:
         if not getattr(head, "is_quantized", False):
             raise ValueError("LlamaMXDecoder needs a quantised lm_head")
         self.vocab = head.packed_weight.shape[0]
-        if self.vocab % w:
-            raise ValueError(f"vocabulary {self.vocab} does not divide over {w} ranks")
-        self.head = rows(head)
+        # the vocabulary projection stays whole on every rank: its input (the residual stream) is replicated, so every
+        # rank gets the full logits and picks the same token without any exchange (70 MB of weights per step at 7B size)
+        self.head = (head.packed_weight, head.weight_scales)
         # rotary tables as the model computes them (float32 angles, cast to the activations' dtype)
         inv_freq = base.rotary_emb.inv_freq.to(self.dev).float()
         scaling = float(getattr(base.rotary_emb, "attention_scaling", 1.0))
@@ -157,22 +157,12 @@ class LlamaMXDecoder:
             x = (self.g_final * F.rms_norm(last.float(), (self.hidden,), eps=self.eps).to(torch.bfloat16)).contiguous()
             c.feed(x)
             c.act(_capi.ACT_IDENTITY, B, self.hidden)
-        logits = torch.empty(B, self.vocab // self.world, dtype=torch.bfloat16, device=self.dev)
+        logits = torch.empty(B, self.vocab, dtype=torch.bfloat16, device=self.dev)
         c.gemm(*self.head, out=logits)
         return logits
 
     def _next_tokens(self, logits):
-        """argmax over the whole vocabulary from every rank's shard of the logits"""
-        val, idx = logits.float().max(dim=-1)
-        idx = idx + self.rank * (self.vocab // self.world)
-        if self.world == 1:
-            return idx
-        mine = torch.stack([val, idx.float()], -1).contiguous()                  # indices < 2^24 are exact in float32
-        allv = [torch.empty_like(mine) for _ in range(self.world)]
-        dist.all_gather(allv, mine, group=self.group)
-        allv = torch.stack(allv, 0)                                               # [world, B, 2]
-        best = allv[..., 0].argmax(dim=0)                                         # first rank wins ties, as one argmax would
-        return allv[..., 1].gather(0, best[None])[0].long()
+        return logits.float().argmax(dim=-1)
 
     @torch.no_grad()
     def prefill(self, prompt_ids: torch.Tensor, chunk: int = 16):
