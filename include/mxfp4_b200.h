@@ -176,6 +176,21 @@ MXFP4_API int mxfp4_gemm_prequantized_ex(const uint8_t* a_packed, const uint8_t*
                                          int64_t splitk_bytes, int* control_block, int flags, void* stream);
 
 /*
+ * W4A16: out[M,N] (bf16) = x[M,K] (bf16, not quantised) . bf16(dequantize(w))[N,K]^T (+ bias), float32 accumulation on the bf16
+ * tensor cores.  The literal arithmetic of the reference's own GEMM paths (FallbackBackend.matmul,
+ * src/mxfp4/backends.py:295-312; Triton quant_matmul, src/mxfp4/fused_kernels.py:141-207): weights decoded inside the
+ * kernel (never materialised in global memory), activations untouched.  Used for scale_format="bf16" weights (their scales
+ * are not powers of two) and, on request, for E8M0 weights when the reference's numerics without activation quantisation
+ * are wanted at a quarter of the FP4 rate.
+ *   w_scales  device, [N, K/block_size] uint8 (MXFP4_SF_E8M0) or bfloat16 (MXFP4_SF_BF16), row-major as the quantiser wrote them
+ *   block_size 16, 32 or 64; K a multiple of 32 and of block_size; x and w_packed 16-byte aligned, ldx*2 a multiple of 16
+ *   status_dev optional device int: receives MXFP4_E_TIMEOUT if a bounded wait ran out
+ */
+MXFP4_API int mxfp4_gemm_w4a16(const void* x_bf16, int64_t ldx, const uint8_t* w_packed, const void* w_scales, int scale_fmt,
+                               int block_size, const void* bias_bf16, void* out_bf16, int64_t ldo, int64_t M, int64_t N,
+                               int64_t K, int* status_dev, void* stream);
+
+/*
  * mxfp4_gemm without any workspace argument and without any device allocation.  It has no counterpart in the
  * reference.  It is for callers that cannot allocate device memory when the matmul is due: a process whose
  * own pool owns the whole GPU and which bans cudaMalloc after start-up, a plugin living inside such a process,

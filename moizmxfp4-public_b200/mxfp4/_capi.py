@@ -78,6 +78,8 @@ def load():
     L.mxfp4_gemm_prequantized.restype = ci
     L.mxfp4_gemm_prequantized_ex.argtypes = [vp, vp, vp, vp, vp, vp, i64, i64, i64, i64, ci, vp, i64, vp, ci, vp]
     L.mxfp4_gemm_prequantized_ex.restype = ci
+    L.mxfp4_gemm_w4a16.argtypes = [vp, i64, vp, vp, ci, ci, vp, vp, i64, i64, i64, i64, vp, vp]
+    L.mxfp4_gemm_w4a16.restype = ci
     L.mxfp4_gemm_plan.argtypes = [i64, i64, i64, ci, ctypes.POINTER(ci), ctypes.POINTER(ci)]
     L.mxfp4_gemm_plan.restype = ci
     L.mxfp4_act_fused.argtypes = [ctypes.POINTER(ActFusedArgs), vp]

@@ -16,7 +16,7 @@ import torch
 
 from . import _capi
 
-_MODES = {"exact": _capi.GEMM_EXACT, "fast": _capi.GEMM_FAST}
+_MODES = {"exact": _capi.GEMM_EXACT, "fast": _capi.GEMM_FAST, "w4a16": -1}
 _mode = _MODES[os.environ.get("MXFP4_GEMM_MODE", "exact")]
 _lock = threading.RLock()
 _PREPARED_MAX = 4096
@@ -30,14 +30,17 @@ def _align(v, a):
 
 
 def set_gemm_mode(mode: str):
-    """"exact" (default): weights decode exactly as the reference dequantises them, two MMAs per K step.
-    "fast": single pass with hardware E2M1 decoding of the weight codes; faster, not parity."""
+    """"exact" (default): FP4 tensor cores, weights decode exactly as the reference dequantises them (two MMAs per K
+    step), activations quantised to MXFP4.
+    "fast": single pass with hardware E2M1 decoding of the weight codes; faster, not parity.
+    "w4a16": the reference's literal arithmetic (bf16 activations left as they are, weights decoded to bf16 inside the
+    kernel, bf16 tensor cores): within bf16 rounding of FallbackBackend.matmul, at a quarter of the FP4 rate."""
     global _mode
     _mode = _MODES[mode]
 
 
 def get_gemm_mode() -> str:
-    return "exact" if _mode == _capi.GEMM_EXACT else "fast"
+    return {_capi.GEMM_EXACT: "exact", _capi.GEMM_FAST: "fast"}.get(_mode, "w4a16")
 
 
 def _cached(src: torch.Tensor, tag, build):
@@ -170,6 +173,13 @@ def check_status(device=None):
         if code != 0:
             ws[:4].zero_()
             raise _capi.MXFP4BackendError(f"mxfp4 GEMM kernel reported status {code} (a device-side wait timed out)")
+    for idx, st in list(_w4a16_status.items()):
+        if device is not None and torch.device(device).index not in (None, idx):
+            continue
+        code = int(st.item())
+        if code != 0:
+            st.zero_()
+            raise _capi.MXFP4BackendError(f"mxfp4 W4A16 GEMM kernel reported status {code} (a device-side wait timed out)")
 
 
 def act_quantize(x: torch.Tensor):
@@ -201,8 +211,8 @@ def quant_matmul_2d(input: torch.Tensor, packed_weight: torch.Tensor, weight_sca
     if packed_weight.dtype != torch.uint8:
         raise TypeError("mxfp4: packed_weight must be uint8")
     block = scale_block_size(weight_scales, N, K)
-    if weight_scales.dtype != torch.uint8:
-        return _matmul_bf16_scales(input, packed_weight, weight_scales, bias, block)
+    if weight_scales.dtype != torch.uint8 or _mode == -1:
+        return matmul_w4a16(input, packed_weight, weight_scales, bias, block, out=out)
     in_dtype = input.dtype
     x = input if in_dtype == torch.bfloat16 else input.to(torch.bfloat16)
     if block == 16:
@@ -397,6 +407,9 @@ class FusedChain:
         """GEMM of the activations the last act() produced with a packed weight [N, K/2].  Without `out` the result
         stays in the chain's own buffer in whatever form is cheapest (bf16, or the partial sums of a K-split) for the
         next act(); with `out` (bf16 [M, N], e.g. a peer-visible partial buffer) it is a finished bf16 matrix."""
+        if _mode < 0:
+            raise _capi.MXFP4BackendError("mxfp4: fused chains run on the FP4 tensor cores (MXFP4 activations); "
+                                          "the W4A16 mode has no activation quantiser to fuse -- set_gemm_mode('exact')")
         M, K = self.act_shape
         N = packed_weight.shape[0]
         assert packed_weight.shape[1] * 2 == K, "activation width does not match the weight"
@@ -430,15 +443,42 @@ class FusedChain:
             raise _capi.MXFP4BackendError(f"mxfp4 fused chain reported status {code} (a device-side wait timed out)")
 
 
-def _matmul_bf16_scales(input, packed_weight, weight_scales, bias, block=32):
-    """scale_format="bf16" weights have no power-of-two scales, so they cannot feed the block-scaled
-    tensor-core path; they take the reference's own formulation (dequantise, cast, dense matmul,
-    src/mxfp4/backends.py:295-312) with this package's dequantiser."""
-    w = _capi.dequantize(packed_weight, weight_scales, block, torch.float32).to(input.dtype)
-    out = torch.matmul(input, w.T)
-    if bias is not None:
-        out += bias
-    return out
+_w4a16_status = {}               # device index -> int32 status word of the W4A16 kernel
+
+
+def matmul_w4a16(input, packed_weight, weight_scales, bias=None, block=32, out=None):
+    """W4A16 GEMM (mxfp4_gemm_w4a16): bf16 activations as they are, weights decoded to bf16 inside the kernel.  The path of
+    scale_format="bf16" weights (no power-of-two scales, so no block-scaled FP4 MMA) and of set_gemm_mode("w4a16");
+    the arithmetic of the reference's FallbackBackend.matmul (src/mxfp4/backends.py:295-312)."""
+    L = _capi.load()
+    M, K = input.shape
+    N = packed_weight.shape[0]
+    dev = input.device
+    if weight_scales.dtype == torch.uint8:
+        fmt = _capi.SF["e8m0"]
+    else:
+        fmt = _capi.SF["bf16"]
+        if weight_scales.dtype != torch.bfloat16:
+            weight_scales = weight_scales.to(torch.bfloat16)
+    in_dtype = input.dtype
+    x = input if in_dtype == torch.bfloat16 else input.to(torch.bfloat16)
+    if x.stride(1) != 1 or (x.stride(0) * 2) % 16 != 0 or x.data_ptr() % 16 != 0:
+        x = x.contiguous()
+    if K % 32 != 0:
+        raise _capi.MXFP4BackendError(f"mxfp4: K={K} must be a multiple of 32 (pad activations to the packed weight's width)")
+    pw, sw = packed_weight.contiguous(), weight_scales.contiguous()
+    b = bias_bf16(bias, dev)
+    if out is None:
+        out = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
+    if M == 0 or N == 0:
+        return out.to(in_dtype)
+    st = _w4a16_status.get(dev.index)
+    if st is None:
+        st = _w4a16_status[dev.index] = torch.zeros(1, dtype=torch.int32, device=dev)
+    with _capi.on_device(dev):
+        _capi.check(L.mxfp4_gemm_w4a16(x.data_ptr(), x.stride(0), pw.data_ptr(), sw.data_ptr(), fmt, block, None if b is None else b.data_ptr(),
+                                       out.data_ptr(), out.stride(0), M, N, K, st.data_ptr(), _capi.stream_ptr(dev)), "mxfp4_gemm_w4a16")
+    return out if in_dtype == torch.bfloat16 else out.to(in_dtype)
 
 
 def mxlinear_forward(input: torch.Tensor, packed_weight: torch.Tensor, weight_scales: torch.Tensor,

@@ -286,7 +286,7 @@ class MXBlockStack(nn.Module):
         eight launches per layer.  fused=False runs the same arithmetic as separate PyTorch operations and layer calls."""
         if fused is None:
             fused = h.is_cuda and h.dtype == torch.bfloat16 and h.dim() == 2 and len(self.layers) > 0 and "qkv" in self.layers[0] \
-                and os.environ.get("MXFP4_STACK_FUSED", "1") != "0"
+                and os.environ.get("MXFP4_STACK_FUSED", "1") != "0" and _gemm.get_gemm_mode() != "w4a16"
         if fused:
             return self._forward_fused(h)
         for L in self.layers:
