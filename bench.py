@@ -792,6 +792,38 @@ def run_decode(args, rank, world, local):
             "gpu_launches": None, "clocks": cs.summary(), "scaling_note": "strong"}
 
 
+def extra_w4a16(local):
+    """The same GEMM shape in W4A16 mode (bf16 activations untouched, weights decoded to bf16 inside the kernel, bf16
+    tensor cores): the reference's literal arithmetic.  Roofline against the measured cuBLAS bf16 rate."""
+    import mxfp4
+    from mxfp4 import gemm
+    from oracle import oracle
+    dev = torch.device("cuda", local)
+    M, N, K = GEMM_M, GEMM_N, GEMM_K
+    packed, scales = mxfp4.MXFP4Quantizer(32, "e8m0").quantize(weight(N, K, 1).to(dev))
+    hx = [torch.randn(M, K, generator=torch.Generator().manual_seed(1000 + M + i)).to(torch.bfloat16) for i in range(2)]
+    xs = [h.to(dev) for h in hx]
+    outs = [torch.empty(M, N, dtype=torch.bfloat16, device=dev) for _ in range(2)]
+    i = [0]
+
+    def run():
+        gemm.matmul_w4a16(xs[i[0] % 2], packed, scales, None, 32, out=outs[i[0] % 2])
+        i[0] += 1
+    ms, n, clk = _timed_loop(run, local, min_s=0.5, batch=10)
+    gemm.check_status()
+    j = (i[0] - 1) % 2
+    rows = torch.cat([torch.tensor([0, M - 1]), torch.randperm(M, generator=torch.Generator().manual_seed(7))[:254]]).unique()
+    ref = oracle.matmul_w4a16(hx[j][rows], packed.cpu(), scales.cpu()).float()
+    y = outs[j][rows.to(dev)].float().cpu()
+    pk = peaks()
+    tf = 2.0 * M * N * K / (ms * 1e-3) / 1e12
+    return {"value": tf, "unit": "TFLOP/s", "ms_per_launch": ms, "launches_timed": n, "kernel": f"gemm_w4a16_kernel<256> [{M}x{N}x{K}]",
+            "parity": {"rows_checked": int(rows.numel()), "rel_fro_w4a16": ((y - ref).norm() / ref.norm()).item(), "max_abs": (y - ref).abs().max().item(),
+                       "tolerance": 1e-2, "oracle": "the reference's literal dequantise-then-matmul (FallbackBackend.matmul)"},
+            "roofline": {"bound": "tensor", "achieved": tf, "peak": pk["bf16_tflops_sustained"], "unit": "TFLOP/s", "frac": tf / pk["bf16_tflops_sustained"],
+                         "peak_source": f"{pk['source']} cuBLAS bf16 sustained"}, "clocks": clk}
+
+
 def extra_llama_decode(args, rank, world, local):
     """Config 4 as a sub-record of the default line: Llama-2-7B-shape greedy decode, tensor-parallel over the ranks."""
     r = run_decode(args, rank, world, local)
@@ -858,6 +890,7 @@ def main():
     if args.workload == "gemm" and not args.no_extras and not args.gemm_shape:
         extra = {}
         for name, fn in (("quantize_dequantize", (lambda: extra_quantize_dequantize(local)) if world == 1 else None),
+                         ("w4a16_gemm", (lambda: extra_w4a16(local)) if world == 1 else None),
                          ("tp_stack", lambda: extra_tp_stack(rank, world, local)),
                          ("llama_decode", lambda: extra_llama_decode(args, rank, world, local))):
             if fn is None:
