@@ -832,8 +832,9 @@ def extra_llama_decode(args, rank, world, local):
             "clocks": r["clocks"]}
 
 
-# DRAM traffic of one GEMM launch (dram__bytes_read.sum + dram__bytes_write.sum, one ncu capture; see profiles/)
-GEMM_TRAFFIC_BYTES = 46.996e6 + 139.78e6      # dram read + write per launch of the bench shape (ncu, profiles/gemm_mxf4_pair_kernel.md)
+# DRAM traffic of one GEMM launch of the bench shape: dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture
+# (two launches: 46.2 / 46.3 MB read, 141.6 / 138.1 MB written)
+GEMM_TRAFFIC_BYTES = 46.25e6 + 139.85e6
 
 
 def main():

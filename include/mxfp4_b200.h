@@ -279,7 +279,15 @@ typedef struct mxfp4_act_fused_args {
     uint8_t* packed;           /* [M, K/2] or NULL */
     uint8_t* sf;               /* blocked scales */
     const void* gamma;         /* bf16 [K] or NULL: the norm's learned weight (RMSNORM) */
+    void* const* peer_results; /* host array [world] of device pointers or NULL: two-shot mode (see below) */
+    uint32_t* owner_count;     /* device uint32, zeroed once (two-shot mode) */
 } mxfp4_act_fused_args;
+/* Two-shot mode of the peer sum (peer_results != NULL, M >= world): the rows are split over the ranks in contiguous chunks of
+ * ceil(M / world); every rank sums, normalises and quantises only ITS rows (reading 1/world of every partial), leaves hidden
+ * state, codes and scales in its peer-visible result block (ceil(M / world) rows of mxfp4_act_fused_result_row_bytes(K) bytes)
+ * and copies the other rows from their owners' blocks: (world-1)/world * 2.3 units of NVLink traffic per rank instead of
+ * world-1, which pays from four ranks up and for prefill-sized M.  No call-site interleaving is assumed in this mode. */
+MXFP4_API int64_t mxfp4_act_fused_result_row_bytes(int64_t K);
 MXFP4_API int mxfp4_act_fused(const mxfp4_act_fused_args* args, void* stream);
 
 #ifdef __cplusplus

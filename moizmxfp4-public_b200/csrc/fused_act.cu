@@ -56,6 +56,11 @@ struct FusedParams {
     uint32_t* epoch;
     long long wait_cycles;
     int wait_done;                    // also wait for the "done" handshake (call sites that are reused back to back)
+    uint8_t* result[kMaxWorld];       // two-shot mode: every rank's peer-visible result block (rows it owns: hidden | codes | scales)
+    int two_shot;                     // rows are split over the ranks; every rank reduces its own rows and fetches the others' results
+    int64_t rows_per;                 // rows a rank owns (the last rank may own fewer)
+    int64_t res_row_bytes;
+    uint32_t* owner_count;            // local device counter of this rank's finished owned rows
     int* status;
     const __nv_bfloat16* bias;        // [K] or null, added to the value
     const __nv_bfloat16* gamma;       // [K] or null (RMSNORM): the norm's learned weight
@@ -136,9 +141,21 @@ __global__ void __launch_bounds__(512) act_fused_kernel(const FusedParams p) {
     // kernel in front of it has completed
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    const int64_t m = blockIdx.x;
     const int64_t kblocks = p.K / 32, chunks = p.K / 8;
     const int tid = threadIdx.x, T = blockDim.x;
+    // Row of this CTA.  In two-shot mode the rows this rank owns come first in launch order: they never wait for another
+    // rank's results, so the CTAs that do wait (for rows other ranks own) cannot keep them off the SMs.
+    int64_t m = blockIdx.x;
+    int owner = p.rank;
+    int64_t own_lo = 0, own_n = 0;
+    if (p.two_shot) {
+        own_lo = p.rows_per * p.rank;
+        own_n = own_lo >= p.M ? 0 : (p.M - own_lo < p.rows_per ? p.M - own_lo : p.rows_per);
+        if ((int64_t)blockIdx.x < own_n) m = own_lo + blockIdx.x;
+        else { m = blockIdx.x - own_n; if (m >= own_lo) m += own_n; }
+        owner = m < p.M ? (int)(m / p.rows_per) : p.rank;
+    }
+    const bool fetch = p.two_shot && m < p.M && owner != p.rank;      // this row's results come from the rank that owns it
 
     uint32_t n = 0;
     if (p.world > 1) {
@@ -153,10 +170,17 @@ __global__ void __launch_bounds__(512) act_fused_kernel(const FusedParams p) {
         if (tid == 0) {
             int ok = 1;
             const long long t0 = clock64();
-            for (int r = 0; r < p.world && ok; ++r) {
-                if (r == p.rank) continue;
-                while ((int32_t)(ld_acquire_sys(my_flags + r) - n) < 0) {
+            if (fetch) {
+                // the owner's "my rows of call n are in my result block"
+                while ((int32_t)(ld_acquire_sys(my_flags + kMaxWorld + owner) - n) < 0) {
                     if (clock64() - t0 > p.wait_cycles) { ok = 0; break; }
+                }
+            } else {
+                for (int r = 0; r < p.world && ok; ++r) {
+                    if (r == p.rank) continue;
+                    while ((int32_t)(ld_acquire_sys(my_flags + r) - n) < 0) {
+                        if (clock64() - t0 > p.wait_cycles) { ok = 0; break; }
+                    }
                 }
             }
             s_ok = ok;
@@ -167,15 +191,32 @@ __global__ void __launch_bounds__(512) act_fused_kernel(const FusedParams p) {
             // memory for activations; the codes become zeros; the status word says why.
             if (tid == 0 && p.status) atomicExch(p.status, MXFP4_E_TIMEOUT);
             if (m < p.M) {
+                // (two-shot: the rows this rank owns go to its result block as NaN too, so the peers that fetch them see it)
+                uint8_t* res = (p.two_shot && !fetch) ? p.result[p.rank] + (m - own_lo) * p.res_row_bytes : nullptr;
                 for (int64_t ci = tid; ci < chunks; ci += T) {
                     if (p.hidden_out) *reinterpret_cast<uint4*>(p.hidden_out + m * p.ld_hid + ci * 8) = make_uint4(0x7FC07FC0u, 0x7FC07FC0u, 0x7FC07FC0u, 0x7FC07FC0u);
                     if (p.packed) *reinterpret_cast<uint32_t*>(p.packed + m * (kblocks * 16) + ci * 4) = 0u;
+                    if (res) {
+                        *reinterpret_cast<uint4*>(res + ci * 16) = make_uint4(0x7FC07FC0u, 0x7FC07FC0u, 0x7FC07FC0u, 0x7FC07FC0u);
+                        *reinterpret_cast<uint32_t*>(res + p.K * 2 + ci * 4) = 0u;
+                    }
                 }
             }
         }
     }
 
-    const bool row_ok = m < p.M && (p.world == 1 || s_ok);
+    if (fetch && s_ok) {
+        // ---- second shot: copy the row's hidden state, codes and scales from the owner's result block over NVLink
+        const uint8_t* src = p.result[owner] + (m - p.rows_per * owner) * p.res_row_bytes;
+        for (int64_t ci = tid; ci < chunks; ci += T) {
+            if (p.hidden_out) *reinterpret_cast<uint4*>(p.hidden_out + m * p.ld_hid + ci * 8) = __ldcg(reinterpret_cast<const uint4*>(src) + ci);
+            if (p.packed) *reinterpret_cast<uint32_t*>(p.packed + m * (kblocks * 16) + ci * 4) = __ldcg(reinterpret_cast<const uint32_t*>(src + p.K * 2) + ci);
+        }
+        if (p.packed)
+            for (int64_t kb = tid; kb < kblocks; kb += T) p.sf[blocked_offset(m, kb, p.kstages)] = __ldcg(src + p.K * 2 + p.K / 2 + kb);
+    }
+    const bool row_ok = m < p.M && !fetch && (p.world == 1 || s_ok);
+    uint8_t* res_row = (p.two_shot && row_ok) ? p.result[p.rank] + (m - own_lo) * p.res_row_bytes : nullptr;
     if (row_ok) {
         uint4 xp[NB];
         float ss = 0.0f;
@@ -203,6 +244,7 @@ __global__ void __launch_bounds__(512) act_fused_kernel(const FusedParams p) {
                     for (int i = 0; i < 8; ++i) ss += x[i] * x[i];
                     xp[it] = pack8(x);
                     if (p.hidden_out) *reinterpret_cast<uint4*>(p.hidden_out + m * p.ld_hid + c) = xp[it];
+                    if (res_row) *reinterpret_cast<uint4*>(res_row + c * 2) = xp[it];
                 } else if (p.op == MXFP4_ACT_SILU_MUL) {
                     float u[8];
                     load_value8(p, m, p.K + c, u);
@@ -269,6 +311,10 @@ __global__ void __launch_bounds__(512) act_fused_kernel(const FusedParams p) {
                     for (int j = 0; j < 4; ++j) word |= cvt_e2m1x2(x[2 * j] * inv, x[2 * j + 1] * inv) << (8 * j);   // even element in the high nibble
                     *reinterpret_cast<uint32_t*>(p.packed + m * (kblocks * 16) + ci * 4) = word;
                     if ((ci & 3) == 0) p.sf[blocked_offset(m, ci >> 2, p.kstages)] = (uint8_t)b;
+                    if (res_row) {
+                        *reinterpret_cast<uint32_t*>(res_row + p.K * 2 + ci * 4) = word;
+                        if ((ci & 3) == 0) res_row[p.K * 2 + p.K / 2 + (ci >> 2)] = (uint8_t)b;
+                    }
                 }
             }
         }
@@ -283,6 +329,19 @@ __global__ void __launch_bounds__(512) act_fused_kernel(const FusedParams p) {
         }
     }
 
+    if (p.two_shot && p.world > 1) {
+        // first shot complete for this row; the last of this rank's owned rows tells every peer that the result block is ready
+        __syncthreads();
+        if (tid == 0 && !fetch && m < p.M) {
+            __threadfence_system();
+            const uint32_t done_rows = atomicAdd(p.owner_count, 1u);
+            if ((int64_t)done_rows == own_n - 1) {
+                *p.owner_count = 0;
+                for (int rr = 0; rr < p.world; ++rr)
+                    if (rr != p.rank) st_release_sys(reinterpret_cast<uint32_t*>(const_cast<uint8_t*>(p.peer[rr])) + kMaxWorld + p.rank, n);
+            }
+        }
+    }
     if (p.world > 1) {
         // the last CTA to get here closes the call: tells the peers that this rank has finished reading, optionally waits
         // for the same from them, then advances the call number
@@ -294,9 +353,10 @@ __global__ void __launch_bounds__(512) act_fused_kernel(const FusedParams p) {
                 // "this rank has finished reading call n" is always published (a plain store per peer), so that the call
                 // site stays usable by launches that do wait for it; the wait itself is optional
                 uint32_t* my_flags = reinterpret_cast<uint32_t*>(const_cast<uint8_t*>(p.peer[p.rank]));
-                for (int rr = 0; rr < p.world; ++rr)
-                    if (rr != p.rank) st_release_sys(reinterpret_cast<uint32_t*>(const_cast<uint8_t*>(p.peer[rr])) + kMaxWorld + p.rank, n);
-                if (p.wait_done) {
+                if (!p.two_shot)
+                    for (int rr = 0; rr < p.world; ++rr)
+                        if (rr != p.rank) st_release_sys(reinterpret_cast<uint32_t*>(const_cast<uint8_t*>(p.peer[rr])) + kMaxWorld + p.rank, n);
+                if (p.wait_done && !p.two_shot) {
                     const long long t0 = clock64();
                     bool ok = true;
                     for (int rr = 0; rr < p.world && ok; ++rr) {
@@ -317,6 +377,11 @@ __global__ void __launch_bounds__(512) act_fused_kernel(const FusedParams p) {
 
 }  // namespace
 }  // namespace mxfp4
+
+extern "C" int64_t mxfp4_act_fused_result_row_bytes(int64_t K) {
+    if (K <= 0) return 0;
+    return K * 2 + K / 2 + (K / 32 + 15) / 16 * 16;          // hidden (bf16) | codes | scale bytes, 16-byte aligned rows
+}
 
 extern "C" int mxfp4_act_fused(const mxfp4_act_fused_args* a, void* stream) {
     using namespace mxfp4;
@@ -370,6 +435,18 @@ extern "C" int mxfp4_act_fused(const mxfp4_act_fused_args* a, void* stream) {
         if (const char* e = getenv("MXFP4_PEER_WAIT_MS")) { const long long v = atoll(e); if (v > 0 && v <= 600000) ms = v; }
         p.wait_cycles = ms * 2000000ll;
         p.wait_done = a->peer_wait_done ? 1 : 0;
+        if (a->peer_results) {
+            // two-shot: needs at least one row per rank and a counter
+            if (!a->owner_count || a->M < p.world) { set_error("mxfp4_act_fused: two-shot mode needs owner_count and M >= world"); return MXFP4_E_BADARG; }
+            for (int r = 0; r < p.world; ++r) {
+                if (!a->peer_results[r] || (uintptr_t)a->peer_results[r] % 16) { set_error("mxfp4_act_fused: result block %d is null or misaligned", r); return MXFP4_E_ALIGN; }
+                p.result[r] = (uint8_t*)a->peer_results[r];
+            }
+            p.two_shot = 1;
+            p.rows_per = (a->M + p.world - 1) / p.world;
+            p.res_row_bytes = mxfp4_act_fused_result_row_bytes(a->K);
+            p.owner_count = a->owner_count;
+        }
     }
     p.status = a->status_dev;
     p.bias = (const __nv_bfloat16*)a->bias; p.gamma = (const __nv_bfloat16*)a->gamma; p.residual = (const __nv_bfloat16*)a->residual; p.ld_res = a->ld_res;

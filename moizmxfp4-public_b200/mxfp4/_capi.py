@@ -27,7 +27,8 @@ class ActFusedArgs(ctypes.Structure):
                 ("world", ctypes.c_int), ("rank", ctypes.c_int), ("epoch", ctypes.c_void_p), ("peer_wait_done", ctypes.c_int),
                 ("status_dev", ctypes.c_void_p), ("bias", ctypes.c_void_p), ("residual", ctypes.c_void_p), ("ld_res", ctypes.c_int64),
                 ("hidden_out", ctypes.c_void_p), ("ld_hid", ctypes.c_int64), ("eps", ctypes.c_float), ("M", ctypes.c_int64),
-                ("K", ctypes.c_int64), ("packed", ctypes.c_void_p), ("sf", ctypes.c_void_p), ("gamma", ctypes.c_void_p)]
+                ("K", ctypes.c_int64), ("packed", ctypes.c_void_p), ("sf", ctypes.c_void_p), ("gamma", ctypes.c_void_p),
+                ("peer_results", ctypes.POINTER(ctypes.c_void_p)), ("owner_count", ctypes.c_void_p)]
 
 
 class MXFP4BackendError(RuntimeError):
@@ -82,6 +83,8 @@ def load():
     L.mxfp4_gemm_w4a16.restype = ci
     L.mxfp4_gemm_plan.argtypes = [i64, i64, i64, ci, ctypes.POINTER(ci), ctypes.POINTER(ci)]
     L.mxfp4_gemm_plan.restype = ci
+    L.mxfp4_act_fused_result_row_bytes.argtypes = [i64]
+    L.mxfp4_act_fused_result_row_bytes.restype = i64
     L.mxfp4_act_fused.argtypes = [ctypes.POINTER(ActFusedArgs), vp]
     L.mxfp4_act_fused.restype = ci
     L.mxfp4_peer_block_bytes.argtypes = [i64, i64]

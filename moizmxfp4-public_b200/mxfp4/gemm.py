@@ -374,6 +374,9 @@ class FusedChain:
             a.peer_blocks, a.world, a.rank = ctypes.cast(peer.blocks, ctypes.POINTER(ctypes.c_void_p)), peer.world, peer.rank
             a.epoch, a.status_dev, a.peer_wait_done = peer.epoch.data_ptr(), peer.status.data_ptr(), 0 if peer.interleaved else 1
             a.ld_in = peer.N
+            if getattr(peer, "results", None) is not None and M >= peer.world and M * peer.N * 2 >= getattr(peer, "two_shot_min_bytes", 0):
+                a.peer_results = ctypes.cast(peer.results, ctypes.POINTER(ctypes.c_void_p))
+                a.owner_count = peer.owner_count.data_ptr()
         elif self.src is not None:
             kind = self.src[0]
             if kind == "bf16":

@@ -118,6 +118,13 @@ class _PeerSum:
         self.rows = 0
         self.N = 0
         self.buf = self.handle = self.blocks = self.epoch = self.status = None
+        self.res = self.res_handle = self.results = self.owner_count = None        # two-shot mode of the fused peer sum
+        # Two-shot (every rank reduces its own rows, then fetches the others' results) moves (world-1)/world * 2.3 partials'
+        # worth of bytes per rank instead of world-1, but adds a second dependent handshake (~14 us measured at two ranks):
+        # it pays from four ranks up and for prefill-sized sums; decode-sized sums (1 MB) stay one-shot.
+        ts = os.environ.get("MXFP4_TP_TWO_SHOT")
+        self.two_shot = (self.world >= 4) if ts is None else ts == "1"
+        self.two_shot_min_bytes = (4 << 20) if ts is None else 0
         self.disabled = os.environ.get("MXFP4_TP_PEER_REDUCE", "1") == "0"
 
     def _make(self, M, N, device):
@@ -134,6 +141,16 @@ class _PeerSum:
         ptrs = [int(v) for v in handle.buffer_ptrs]
         self.blocks = (ctypes.c_void_p * len(ptrs))(*ptrs)
         self.buf, self.handle, self.rows, self.N = buf, handle, rows, N
+        if self.two_shot:
+            # result block: the rows this rank owns (at most ceil(rows / world)) as hidden | codes | scales
+            res = symm.empty(-(-rows // self.world) * L.mxfp4_act_fused_result_row_bytes(N), dtype=torch.uint8, device=device)
+            res_handle = symm.rendezvous(res, group)
+            rptrs = [int(v) for v in res_handle.buffer_ptrs]
+            self.results = (ctypes.c_void_p * len(rptrs))(*rptrs)
+            self.res, self.res_handle = res, res_handle
+            self.owner_count = torch.zeros(1, dtype=torch.int32, device=device)
+            torch.cuda.synchronize(device)
+            dist.barrier(group=group)
         self.epoch = torch.zeros(2, dtype=torch.int32, device=device)
         self.status = torch.zeros(1, dtype=torch.int32, device=device)
 

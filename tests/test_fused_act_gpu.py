@@ -145,6 +145,79 @@ def test_rmsnorm_over_peer_blocks_is_the_all_reduce(monkeypatch, world):
     assert torch.equal(torch.ones(4, device=dev) * 2, torch.full((4,), 2.0, device=dev))
 
 
+def test_two_shot_peer_sum_with_emulated_ranks(monkeypatch):
+    """Two-shot mode on one GPU: rank 0 reduces, normalises and quantises the rows it owns and leaves them in its result
+    block; the rows the other 'ranks' own are copied from their result blocks (filled by hand here, their flags set as
+    their launches would set them)."""
+    from mxfp4 import _capi
+    L = _capi.load()
+    dev = torch.device("cuda", 0)
+    world, M, K = 4, 90, 512
+    rows_per = -(-M // world)                                   # 23: ranks own 23, 23, 23, 21 rows
+    off = L.mxfp4_peer_partial_offset()
+    rb = L.mxfp4_act_fused_result_row_bytes(K)
+    assert rb == K * 2 + K // 2 + 16
+    blocks = [torch.zeros(L.mxfp4_peer_block_bytes(M, K), dtype=torch.uint8, device=dev) for _ in range(world)]
+    results = [torch.zeros(rows_per * rb, dtype=torch.uint8, device=dev) for _ in range(world)]
+    parts = [act(M, K, 50 + r).to(dev) for r in range(world)]
+    for b, p_ in zip(blocks, parts):
+        b[off:off + M * K * 2].view(torch.bfloat16).view(M, K).copy_(p_)
+    # what the other ranks "computed" for their rows: recognisable hidden values, codes and scales
+    fake_h = act(M, K, 99).to(dev)
+    fake_codes = torch.randint(0, 256, (M, K // 2), generator=torch.Generator().manual_seed(5), dtype=torch.uint8).to(dev)
+    fake_sc = torch.randint(100, 140, (M, K // 32), generator=torch.Generator().manual_seed(6), dtype=torch.uint8).to(dev)
+    for r in range(1, world):
+        for m in range(r * rows_per, min(M, (r + 1) * rows_per)):
+            row = results[r][(m - r * rows_per) * rb:(m - r * rows_per + 1) * rb]
+            row[:K * 2].copy_(fake_h[m].view(torch.uint8))
+            row[K * 2:K * 2 + K // 2].copy_(fake_codes[m])
+            row[K * 2 + K // 2:K * 2 + K // 2 + K // 32].copy_(fake_sc[m])
+    flags0 = blocks[0][:off].view(torch.int32)
+    for r in range(1, world):
+        flags0[r] = 1          # ready
+        flags0[8 + r] = 1      # the rank's rows are in its result block
+    arr = (ctypes.c_void_p * world)(*[b.data_ptr() for b in blocks])
+    rarr = (ctypes.c_void_p * world)(*[b.data_ptr() for b in results])
+    epoch = torch.zeros(2, dtype=torch.int32, device=dev)
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    count = torch.zeros(1, dtype=torch.int32, device=dev)
+    res = act(M, K, 9).to(dev)
+    a = _capi.ActFusedArgs()
+    a.op, a.M, a.K, a.eps = _capi.ACT_RMSNORM, M, K, 1e-6
+    a.peer_blocks, a.world, a.rank = ctypes.cast(arr, ctypes.POINTER(ctypes.c_void_p)), world, 0
+    a.epoch, a.status_dev, a.ld_in = epoch.data_ptr(), status.data_ptr(), K
+    a.peer_results, a.owner_count = ctypes.cast(rarr, ctypes.POINTER(ctypes.c_void_p)), count.data_ptr()
+    a.residual, a.ld_res = res.data_ptr(), K
+    hid = torch.zeros(M, K, dtype=torch.bfloat16, device=dev)
+    packed = torch.zeros(M, K // 2, dtype=torch.uint8, device=dev)
+    sf = torch.full((L.mxfp4_act_scales_bytes(M, K),), 255, dtype=torch.uint8, device=dev)
+    a.hidden_out, a.ld_hid, a.packed, a.sf = hid.data_ptr(), K, packed.data_ptr(), sf.data_ptr()
+    monkeypatch.setenv("MXFP4_PEER_WAIT_MS", "500")
+    _capi.check(L.mxfp4_act_fused(ctypes.byref(a), None), "mxfp4_act_fused")
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0 and int(epoch[0].item()) == 1 and int(count.item()) == 0
+    own = slice(0, rows_per)
+    acc = torch.zeros(M, K, dtype=torch.float32, device=dev)
+    for p_ in parts:
+        acc = acc + p_.float()
+    h_ref = res + acc.to(torch.bfloat16)
+    assert torch.equal(hid[own], h_ref[own])                                        # first shot: this rank's rows
+    assert torch.equal(hid[rows_per:], fake_h[rows_per:])                           # second shot: fetched rows
+    assert torch.equal(packed[rows_per:], fake_codes[rows_per:])
+    sc = unblock(sf, M, K)
+    assert torch.equal(sc[rows_per:], fake_sc[rows_per:].cpu())
+    op, os_ = oracle.act_quantize(torch.nn.functional.rms_norm(h_ref[own], (K,), eps=1e-6).cpu())
+    assert (packed[own].cpu() == op).float().mean().item() > 0.995 and (sc[own] == os_).float().mean().item() > 0.995
+    # this rank's result block holds exactly what it wrote locally, and the peers were told
+    mine = results[0].view(rows_per, rb)
+    assert torch.equal(mine[:, :K * 2].contiguous().view(torch.bfloat16).view(rows_per, K), hid[own])
+    assert torch.equal(mine[:, K * 2:K * 2 + K // 2], packed[own])
+    assert torch.equal(mine[:, K * 2 + K // 2:K * 2 + K // 2 + K // 32].cpu(), sc[own])
+    for r in range(1, world):
+        fl = blocks[r][:off].view(torch.int32)
+        assert int(fl[0].item()) == 1 and int(fl[8].item()) == 1
+
+
 def test_argument_checks():
     from mxfp4 import _capi
     L = _capi.load()

@@ -143,7 +143,7 @@ def test_quant_matmul_argument_contract():
         quant_matmul(torch.zeros(4, 128, dtype=torch.bfloat16), op, os_)
 
 
-def test_bf16_scale_weights_take_the_dense_side_path():
+def test_bf16_scale_weights_take_the_w4a16_kernel():
     from mxfp4 import quant_matmul
     w = weight(96, 256, 4, True)
     x = act(8, 256, 3)

@@ -76,6 +76,17 @@ def _worker(rank, world, port, q):
         # the fused layers may pick another K-split, i.e. another float32 summation order: equal up to bf16 rounding
         assert ((out.float() - unfused.float()).norm() / unfused.float().norm()).item() < 2e-3
         gemm.check_status()
+        # the other mode of the fused peer sum (one-shot: every rank reads all partials; two-shot: every rank reduces its
+        # own rows and fetches the others' results) computes every row with the same arithmetic: same bits
+        default_two_shot = stack.layers[0]["o"]._peer.two_shot
+        os.environ["MXFP4_TP_TWO_SHOT"] = "0" if default_two_shot else "1"
+        try:
+            other = MXBlockStack.build(n_layers=2, device=dev)
+            out_other = other(xin)
+            assert other.layers[0]["o"]._peer.two_shot != default_two_shot
+        finally:
+            os.environ.pop("MXFP4_TP_TWO_SHOT")
+        assert torch.equal(out, out_other)
         fin = bool(torch.isfinite(out.float()).all().item())
         ref = [torch.empty_like(out) for _ in range(world)]
         dist.all_gather(ref, out)
