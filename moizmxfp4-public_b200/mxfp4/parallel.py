@@ -121,10 +121,11 @@ class _PeerSum:
         self.res = self.res_handle = self.results = self.owner_count = None        # two-shot mode of the fused peer sum
         # Two-shot (every rank reduces its own rows, then fetches the others' results) moves (world-1)/world * 2.3 partials'
         # worth of bytes per rank instead of world-1, but adds a second dependent handshake (~14 us measured at two ranks):
-        # it pays from four ranks up and for prefill-sized sums; decode-sized sums (1 MB) stay one-shot.
+        # at four ranks it still loses on 16 MB sums (12.3 against 11.4 ms per 2048-token prefill of the 32-layer stack), so it
+        # is the default only at eight ranks (prefill of 2048 tokens 17.6 -> 11.8 ms, decode step 4.18 -> 4.05 ms).
         ts = os.environ.get("MXFP4_TP_TWO_SHOT")
-        self.two_shot = (self.world >= 4) if ts is None else ts == "1"
-        self.two_shot_min_bytes = (4 << 20) if ts is None else 0
+        self.two_shot = (self.world >= 8) if ts is None else ts == "1"
+        self.two_shot_min_bytes = 0
         self.disabled = os.environ.get("MXFP4_TP_PEER_REDUCE", "1") == "0"
 
     def _make(self, M, N, device):
