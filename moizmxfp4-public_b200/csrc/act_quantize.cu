@@ -44,7 +44,17 @@ __global__ void __launch_bounds__(256) act_quantize_kernel(const uint8_t* __rest
     const int64_t kb_pad = kstages * 8;
     const int64_t idx = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
     if (idx >= m_pad * kb_pad) return;
-    const int64_t row = idx / kb_pad, kb = idx - row * kb_pad;
+    int64_t row, kb;
+    if (m_pad * kb_pad < 0x7FFFFFFFll) {
+        // 32-bit index arithmetic whenever the block grid allows it: a 64-bit division per thread costs about as many
+        // instructions as the rest of the kernel
+        const uint32_t r32 = (uint32_t)idx / (uint32_t)kb_pad;
+        row = r32;
+        kb = (uint32_t)idx - r32 * (uint32_t)kb_pad;
+    } else {
+        row = idx / kb_pad;
+        kb = idx - row * kb_pad;
+    }
     uint32_t byte = 0;
     if (row < M && kb < kblocks) {
         uint32_t w[16];

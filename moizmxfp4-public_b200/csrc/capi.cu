@@ -1,4 +1,5 @@
 // Library-level entry points of the C ABI: version, error text, device query.
+#include <atomic>
 #include <cstdarg>
 #include <cstring>
 
@@ -16,7 +17,7 @@ void set_error(const char* fmt, ...) {
 }
 
 int num_sms() {
-    static int cached[64] = {0};
+    static std::atomic<int> cached[64];      // per device; every writer stores the same value
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
     if (cached[dev] == 0) {

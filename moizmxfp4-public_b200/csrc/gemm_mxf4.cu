@@ -20,6 +20,7 @@
 // 6..9 = epilogue, 10 and 16 = scale-factor copiers.
 // Every wait is bounded; a wait that runs out records MXFP4_E_TIMEOUT in the status word and the
 // CTA drains and exits.
+#include <atomic>
 #include <cstdlib>
 
 #include "gemm_mxf4_tc.cuh"
@@ -488,14 +489,14 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
 EncodeTiledFn encode_fn() {
-    static EncodeTiledFn fn = nullptr;
-    if (!fn) {
+    static std::atomic<EncodeTiledFn> fn{nullptr};
+    if (!fn.load()) {
         void* ptr = nullptr;
         cudaDriverEntryPointQueryResult qres;
         if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess && qres == cudaDriverEntryPointSuccess)
-            fn = (EncodeTiledFn)ptr;
+            fn.store((EncodeTiledFn)ptr);
     }
-    return fn;
+    return fn.load();
 }
 
 // Byte matrix [rows, row_bytes] (row pitch = row_bytes), box = 128 bytes x box_rows, 128-byte swizzle,
@@ -532,7 +533,7 @@ int make_out_map(CUtensorMap* map, const void* ptr, int64_t rows, int64_t cols, 
 template <int BN>
 int launch_gemm(const CUtensorMap& mw, const CUtensorMap& mx, GemmParams& p, cudaStream_t st) {
     using C = Cfg<BN>;
-    static bool configured[64] = {false};
+    static std::atomic<bool> configured[64];
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev >= 0 && dev < 64 && !configured[dev]) {
@@ -814,7 +815,7 @@ extern "C" int mxfp4_gemm_noalloc(const void* x_bf16, int64_t ldx, const uint8_t
     }
     // The array's name is only a host-side handle; the kernels need its device address, which differs per
     // device.  Looked up once per device, with that device current (it is: the caller made it current).
-    static unsigned char* scratch_addr[64] = {nullptr};
+    static std::atomic<unsigned char*> scratch_addr[64];
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return cuda_fail(e, "mxfp4_gemm_noalloc: cudaGetDevice");

@@ -25,6 +25,7 @@
 //    back, and only then transpose through shared memory and store, as TMA tile stores when the output is aligned.
 // Every wait is bounded as in the one-CTA kernel; both CTAs meet at a cluster barrier before they exit, so no
 // remote arrival can target a CTA that has gone.
+#include <atomic>
 #include "gemm_mxf4_tc.cuh"
 
 namespace mxfp4 {
@@ -566,7 +567,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
 template <int BN>
 int launch_pair(const CUtensorMap& mw, const CUtensorMap& mx, const CUtensorMap& mo, GemmParams& p, cudaStream_t st) {
     using C = PairCfg<BN>;
-    static int clusters[64] = {0};       // co-resident CTA pairs per device, 0 = not configured yet
+    static std::atomic<int> clusters[64];       // co-resident CTA pairs per device, 0 = not configured yet
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev < 0 || dev >= 64) { set_error("mxfp4_gemm: device index out of range"); return MXFP4_E_CUDA; }
@@ -589,7 +590,8 @@ int launch_pair(const CUtensorMap& mw, const CUtensorMap& mx, const CUtensorMap&
     }
     p.m_tiles = (p.M + BN - 1) / BN;
     const int64_t units = (int64_t)((p.n_tiles + 1) / 2) * p.m_tiles;
-    const int pairs = (int)(units < clusters[dev] ? units : clusters[dev]);
+    const int64_t resident = clusters[dev].load();
+    const int pairs = (int)(units < resident ? units : resident);
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)(2 * pairs), 1, 1);
     cfg.blockDim = dim3(kPairThreads, 1, 1);

@@ -16,6 +16,7 @@
 // memory (no scale factors live there for kind::f16), so the epilogue of a tile overlaps the next tile's MMAs.
 // Tile: 128 weight rows (MMA M) x BN activation rows (MMA N) x 64 elements of K per stage (one 128-byte swizzle span of
 // bf16), 4 MMAs of K = 16 per stage.  Persistent grid, one CTA per SM.  Every wait is bounded as in the FP4 kernels.
+#include <atomic>
 #include "gemm_mxf4_tc.cuh"
 
 namespace mxfp4 {
@@ -309,19 +310,20 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
 // bf16 matrix [rows, cols] with row pitch ld elements, boxes of 64 elements (128 bytes) x box_rows, 128-byte swizzle,
 // out-of-range parts of a box read as zero
 int make_x_map(CUtensorMap* map, const void* ptr, int64_t rows, int64_t cols, int64_t ld, int box_rows) {
-    static EncodeTiledFn fn = nullptr;
-    if (!fn) {
+    static std::atomic<EncodeTiledFn> fn{nullptr};
+    if (!fn.load()) {
         void* f = nullptr;
         cudaDriverEntryPointQueryResult qres;
         if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &qres) == cudaSuccess && qres == cudaDriverEntryPointSuccess)
-            fn = (EncodeTiledFn)f;
+            fn.store((EncodeTiledFn)f);
     }
-    if (!fn) { set_error("cuTensorMapEncodeTiled is not available from this driver"); return MXFP4_E_CUDA; }
+    EncodeTiledFn enc = fn.load();
+    if (!enc) { set_error("cuTensorMapEncodeTiled is not available from this driver"); return MXFP4_E_CUDA; }
     cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
     cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
     cuuint32_t box[2] = {(cuuint32_t)kWStageK, (cuuint32_t)box_rows};
     cuuint32_t estr[2] = {1, 1};
-    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                     CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) { set_error("cuTensorMapEncodeTiled (bf16 activations) failed with CUresult %d", (int)r); return MXFP4_E_CUDA; }
     return MXFP4_OK;
@@ -330,7 +332,7 @@ int make_x_map(CUtensorMap* map, const void* ptr, int64_t rows, int64_t cols, in
 template <int BN>
 int launch_w4a16(const CUtensorMap& mx, W4A16Params& p, cudaStream_t st) {
     using C = WCfg<BN>;
-    static bool configured[64] = {false};
+    static std::atomic<bool> configured[64];
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev >= 0 && dev < 64 && !configured[dev]) {
