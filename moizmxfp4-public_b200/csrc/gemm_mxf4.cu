@@ -615,10 +615,7 @@ int pick_ksplit(int64_t M, int64_t N, int64_t K) { return pick_plan(M, N, K).ksp
 int pick_pair_bn(int64_t M, int64_t N, bool exact) {
     const char* e = getenv("MXFP4_GEMM_PAIR");
     const int forced = e ? atoi(e) : -1;
-#ifndef MXFP4_PAIR_MIN_M
-#define MXFP4_PAIR_MIN_M 512
-#endif
-    if (forced == 0 || M < MXFP4_PAIR_MIN_M || N < 256) return 0;
+    if (forced == 0 || M < 512 || N < 256) return 0;
     if (forced < 0) {
         const bool use = exact ? (M >= 768 || N >= 16384) : (M >= 1024 && M <= 2048 && N <= 12288);
         if (!use) return 0;

@@ -90,8 +90,9 @@ __device__ __forceinline__ uint32_t make_idesc_pair(int n, uint32_t sf_id) {
 // correction transform (EXACT mode)
 // Measured on the 8192 x 11008 x 4096 problem, sustained: the second MMA issuer on warp 18 instead of warp 15 (another
 // warp scheduler than before: the two issuers and the producer now sit on three different schedulers) +2.5 %; 4
-// transform warps instead of 8 -1 %; 16 epilogue warps (64 columns each) +1.6 % but they need the shared memory of the
-// third correction tile, which costs 3.5 %; 32-column tensor-memory loads in the epilogue -1 % (spills); a suspend-time
+// transform warps instead of 8 -1 %; 16 epilogue warps (64 columns each) -2 % at equal ring depths; two correction tiles
+// instead of three -3.5 %, four tiles with four operand slots instead of three with five +3 % (kept), five or six tiles
+// with four or three slots -1.5 % / -4 %; 32-column tensor-memory loads in the epilogue -1 % (spills); a suspend-time
 // hint on mbarrier.try_wait (fewer polling instructions) -1 %.
 constexpr int kTransformWarps = 8;
 constexpr int kEpiWarps = 8;                         // two per lane quarter
@@ -136,7 +137,7 @@ struct PairCfg {
     static constexpr int kXBytes = kHalf * kStageKBytes;
     static constexpr int kOffX = kWBytes;
     static constexpr int kStageBytes = kWBytes + kXBytes;          // a pipeline slot holds the two operand tiles only
-    static constexpr int kCorrBufs = 3;                            // ring of correction tiles (EXACT mode)
+    static constexpr int kCorrBufs = 4;                            // ring of correction tiles (EXACT mode)
     static constexpr int kCorrBytes = kCorrBufs * kWBytes;
     static constexpr int kEpiBytes = kEpiWarps * 2048;             // per epilogue warp: 32 x 32 bf16 for the transpose
     static constexpr int kEpiCols = BN / kEpiGroups;               // accumulator columns one epilogue warp drains
@@ -150,7 +151,8 @@ struct PairCfg {
     static constexpr int kColSfx = kColSf + 16;    // 2 K-tiles x 4*kXT columns
     static constexpr int kBudget = 227 * 1024 - 1024 - 1024 - kEpiBytes - kCorrBytes;
     static constexpr int kBySmem = kBudget / kStageBytes;
-    static constexpr int kStages = kBySmem < 8 ? kBySmem : 8;
+    // four operand slots and four correction tiles: measured 3 % faster than five slots and three tiles (same shared memory)
+    static constexpr int kStages = kBySmem < 4 ? kBySmem : 4;
     static constexpr int kByTmem = (512 - kColSf) / kSfSetCols;
     static constexpr int kSfSets = kByTmem < 8 ? kByTmem : 8;      // a deeper ring than the operand pipeline: the peer's reports get a head start
     static constexpr int kSmemBytes = kStages * kStageBytes + kCorrBytes + kEpiBytes + 1024 + 1024;
