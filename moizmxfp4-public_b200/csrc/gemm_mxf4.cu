@@ -36,7 +36,8 @@ struct Cfg {
     static constexpr int kSfwBytes = 2048;
     static constexpr int kSfxBytes = 1024 * kXT;
     static constexpr int kOffX = kWBytes;
-    static constexpr int kCorrBufs = 2;                            // correction tiles live in a small ring of their own, so that a
+    // decode-sized tiles have room for four correction tiles beside four pipeline slots (4-5 % on [128, 12288..22016, 4096])
+    static constexpr int kCorrBufs = BN <= 128 ? 4 : 2;            // correction tiles live in a small ring of their own, so that a
     static constexpr int kCorrBytes = kCorrBufs * kWBytes;         // pipeline slot only holds what TMA delivers (more slots in flight)
     static constexpr int kOffSfw = kOffX + kXBytes;
     static constexpr int kOffSfx = kOffSfw + kSfwBytes;
