@@ -817,7 +817,7 @@ def extra_w4a16(local):
     y = outs[j][rows.to(dev)].float().cpu()
     pk = peaks()
     tf = 2.0 * M * N * K / (ms * 1e-3) / 1e12
-    return {"value": tf, "unit": "TFLOP/s", "ms_per_launch": ms, "launches_timed": n, "kernel": f"gemm_w4a16_kernel<256> [{M}x{N}x{K}]",
+    return {"value": tf, "unit": "TFLOP/s", "ms_per_launch": ms, "launches_timed": n, "kernel": f"gemm_w4a16_kernel<256, 1> [{M}x{N}x{K}]",
             "parity": {"rows_checked": int(rows.numel()), "rel_fro_w4a16": ((y - ref).norm() / ref.norm()).item(), "max_abs": (y - ref).abs().max().item(),
                        "tolerance": 1e-2, "oracle": "the reference's literal dequantise-then-matmul (FallbackBackend.matmul)"},
             "roofline": {"bound": "tensor", "achieved": tf, "peak": pk["bf16_tflops_sustained"], "unit": "TFLOP/s", "frac": tf / pk["bf16_tflops_sustained"],

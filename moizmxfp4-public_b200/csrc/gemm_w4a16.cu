@@ -14,8 +14,8 @@
 // current one is decoded), build the bf16 tile in shared memory in the 128-byte-swizzled layout the tensor core reads, and
 // hand it to the MMA thread through an mbarrier.  Activations arrive by TMA.  Accumulators are double-buffered in tensor
 // memory (no scale factors live there for kind::f16), so the epilogue of a tile overlaps the next tile's MMAs.
-// Tile: 128 weight rows (MMA M) x BN activation rows (MMA N) x 64 elements of K per stage (one 128-byte swizzle span of
-// bf16), 4 MMAs of K = 16 per stage.  Persistent grid, one CTA per SM.  Every wait is bounded as in the FP4 kernels.
+// Tile: WT x 128 weight rows (MMA M = 128 each) x BN activation rows (MMA N) x 64 elements of K per stage (one 128-byte
+// swizzle span of bf16), 4 x WT MMAs of K = 16 per stage.  Persistent grid, one CTA per SM.  Every wait is bounded as in the FP4 kernels.
 #include <atomic>
 #include "gemm_mxf4_tc.cuh"
 
@@ -25,17 +25,20 @@ namespace {
 constexpr int kWThreads = 448;      // warps: 0 TMA producer, 1 MMA issuer (owns tensor memory), 2-9 weight decoders, 10-13 epilogue
 constexpr int kWStageK = 64;        // elements of K per stage
 
-template <int BN>
+// WT weight tiles of 128 rows share one activation tile.  Only WT = 1 is instantiated: two weight tiles against a
+// 128-row activation tile need a third less L2 traffic than one against 256 rows, but measured 527 against 891 TFLOP/s
+// on [8192, 11008, 4096] (MMAs of 128 columns read their operands from shared memory at twice the rate per flop).
+template <int BN, int WT>
 struct WCfg {
-    static constexpr int kABytes = kTileW * 128;                 // decoded weight tile: 128 rows x 64 bf16
+    static constexpr int kABytes = kTileW * 128;                 // one decoded weight tile: 128 rows x 64 bf16
     static constexpr int kBBytes = BN * 128;                     // activation tile: BN rows x 64 bf16
-    static constexpr int kStageBytes = kABytes + kBBytes;
+    static constexpr int kStageBytes = WT * kABytes + kBBytes;
     static constexpr int kEpiBytes = 4 * 4096;
     static constexpr int kBudget = 227 * 1024 - 1024 - 512 - kEpiBytes;
     static constexpr int kStages = (kBudget / kStageBytes) < 6 ? (kBudget / kStageBytes) : 6;
     static constexpr int kSmemBytes = kStages * kStageBytes + kEpiBytes + 1024 + 512;
     static constexpr int kAccStride = 256;                       // two accumulators of up to 256 columns
-    static_assert(BN % 32 == 0 && BN <= 256 && kStages >= 2 && kStageBytes % 1024 == 0, "tile width");
+    static_assert(BN % 32 == 0 && WT * BN <= 256 && kStages >= 2 && kStageBytes % 1024 == 0, "tile width");
 };
 
 struct W4A16Params {
@@ -46,7 +49,7 @@ struct W4A16Params {
     __nv_bfloat16* out;
     int64_t ldo;
     int M, N, K;
-    int kstages, n_tiles, m_tiles;
+    int kstages, n_tiles, n_supers, m_tiles;      // n_supers: groups of WT weight tiles
     int* status;
 };
 
@@ -66,47 +69,54 @@ __device__ __forceinline__ void tc_mma_bf16(uint32_t d_tmem, uint64_t adesc, uin
 
 // what one decoder thread needs for one (row, 32-element block) of a stage
 struct WBlock {
-    uint4 codes;        // 16 bytes = 32 codes
-    float s0, s1;       // scale of elements 0-15 and 16-31 (they differ only for block_size 16)
+    uint4 codes;               // 16 bytes = 32 codes
+    __nv_bfloat162 s0, s1;     // scale of elements 0-15 and 16-31 in both halves (they differ only for block_size 16)
 };
 
-__device__ __forceinline__ float scale_value(const W4A16Params& p, int64_t idx) {
-    if (p.scale_fmt == MXFP4_SF_E8M0) return e8m0_value(__ldg(reinterpret_cast<const uint8_t*>(p.w_scales) + idx));
-    return __bfloat162float(__ldg(reinterpret_cast<const __nv_bfloat16*>(p.w_scales) + idx));
+// A scale as a bf16 pair.  Exact: a bf16 scale is taken as it is, 2^(byte-127) is a bf16 value for every byte (a
+// subnormal one for byte 0).
+__device__ __forceinline__ __nv_bfloat162 scale_pair(const W4A16Params& p, int64_t idx) {
+    if (p.scale_fmt == MXFP4_SF_E8M0) return __float2bfloat162_rn(e8m0_value(__ldg(reinterpret_cast<const uint8_t*>(p.w_scales) + idx)));
+    return __bfloat162bfloat162(__ldg(reinterpret_cast<const __nv_bfloat16*>(p.w_scales) + idx));
 }
 
-__device__ __forceinline__ WBlock load_wblock(const W4A16Params& p, int n, int k0) {     // k0: first element of the block, multiple of 32
+// k0: first element of the block, a multiple of 32; block_shift = log2(block size)
+__device__ __forceinline__ WBlock load_wblock(const W4A16Params& p, int block_shift, int n, int k0) {
     WBlock b;
     b.codes = make_uint4(0, 0, 0, 0);
-    b.s0 = b.s1 = 0.0f;             // rows past N and blocks past K decode to zero
+    b.s0 = b.s1 = __float2bfloat162_rn(0.0f);             // rows past N and blocks past K decode to zero
     if (n < p.N && k0 < p.K) {
-        b.codes = __ldg(reinterpret_cast<const uint4*>(p.w_packed + (int64_t)n * (p.K / 2) + k0 / 2));
-        const int64_t per_row = p.K / p.block;
-        b.s0 = scale_value(p, (int64_t)n * per_row + k0 / p.block);
-        b.s1 = p.block == 16 ? scale_value(p, (int64_t)n * per_row + k0 / 16 + 1) : b.s0;
+        b.codes = __ldg(reinterpret_cast<const uint4*>(p.w_packed + (int64_t)n * (p.K >> 1) + (k0 >> 1)));
+        const int64_t first = (int64_t)n * (p.K >> block_shift) + (k0 >> block_shift);
+        b.s0 = scale_pair(p, first);
+        b.s1 = block_shift == 4 ? scale_pair(p, first + 1) : b.s0;
     }
     return b;
 }
 
-// four code bytes (8 elements, even element in the high nibble) -> four bf16 pairs: bf16(level * scale), as the
-// reference's dequantize() followed by the cast to the activations' dtype gives them
-__device__ __forceinline__ uint4 decode8(uint32_t w, float s) {
-    uint32_t o[4];
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-        const uint32_t byte = (w >> (8 * j)) & 0xFFu;
-        const uint32_t hi = byte >> 4, lo = byte & 15u;
-        const float a = ref_level(hi & 7u) * ((hi & 8u) ? -s : s);
-        const float b = ref_level(lo & 7u) * ((lo & 8u) ? -s : s);
-        const __nv_bfloat162 y = __floats2bfloat162_rn(a, b);
-        o[j] = *reinterpret_cast<const uint32_t*>(&y);
-    }
-    return make_uint4(o[0], o[1], o[2], o[3]);
+// Four code bytes (8 elements, even element in the high nibble) -> four bf16 pairs: bf16(level * scale), as the
+// reference's dequantize() followed by the cast to the activations' dtype gives them.  The level of a code c = e<<1 | m
+// is (1 + m/2) * 2^(e-1), whose bf16 pattern is 0x3F00 + (c << 6) with the nibble's sign bit moved to bit 15.  Two
+// nibbles sit in the two 16-bit lanes of a word; one multiply by 0x1040 places copies at bit 6 and at bit 12 of each
+// lane, a mask keeps magnitude and sign.  The product with the scale is one bf16x2 multiply: level and scale have at
+// most 2 and 8 significant bits, so rounding the exact product once to bf16 is the float32 multiply followed by the
+// cast.  The lanes hold elements (0,4), (1,5), (2,6), (3,7); byte permutes put neighbours side by side again.
+__device__ __forceinline__ uint32_t levels_times_scale(uint32_t lanes, __nv_bfloat162 s2) {
+    const uint32_t lv = ((lanes * 0x1040u) & 0x81C081C0u) + 0x3F003F00u;
+    const __nv_bfloat162 y = __hmul2(*reinterpret_cast<const __nv_bfloat162*>(&lv), s2);
+    return *reinterpret_cast<const uint32_t*>(&y);
+}
+__device__ __forceinline__ uint4 decode8(uint32_t w, __nv_bfloat162 s2) {
+    const uint32_t r04 = levels_times_scale((w >> 4) & 0x000F000Fu, s2);
+    const uint32_t r15 = levels_times_scale(w & 0x000F000Fu, s2);
+    const uint32_t r26 = levels_times_scale((w >> 12) & 0x000F000Fu, s2);
+    const uint32_t r37 = levels_times_scale((w >> 8) & 0x000F000Fu, s2);
+    return make_uint4(__byte_perm(r04, r15, 0x5410), __byte_perm(r26, r37, 0x5410), __byte_perm(r04, r15, 0x7632), __byte_perm(r26, r37, 0x7632));
 }
 
-template <int BN>
+template <int BN, int WT>
 __global__ void __launch_bounds__(kWThreads, 1) gemm_w4a16_kernel(const __grid_constant__ CUtensorMap map_x, const W4A16Params p) {
-    using C = WCfg<BN>;
+    using C = WCfg<BN, WT>;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;                 // 128-byte swizzle wants 1024-byte aligned tiles
@@ -123,7 +133,7 @@ __global__ void __launch_bounds__(kWThreads, 1) gemm_w4a16_kernel(const __grid_c
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tail + 4);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int total_units = p.n_tiles * p.m_tiles;
+    const int total_units = p.n_supers * p.m_tiles;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < C::kStages; ++s) {
@@ -154,13 +164,13 @@ __global__ void __launch_bounds__(kWThreads, 1) gemm_w4a16_kernel(const __grid_c
             uint32_t it = 0;
             bool ok = true;
             for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x) {
-                const int m0 = (u / p.n_tiles) * BN;
+                const int m0 = (u / p.n_supers) * BN;
                 for (int ks = 0; ks < p.kstages; ++ks, ++it) {
                     const int s = it % C::kStages;
                     const uint32_t ph = (it / C::kStages) & 1;
                     if (!mbar_wait(empty_bar(s), ph ^ 1u, abort_flag)) { ok = false; break; }
                     mbar_expect_tx(x_full_bar(s), C::kBBytes);
-                    tma_load_2d(base + s * C::kStageBytes + C::kABytes, &map_x, x_full_bar(s), ks * kWStageK, m0);
+                    tma_load_2d(base + s * C::kStageBytes + WT * C::kABytes, &map_x, x_full_bar(s), ks * kWStageK, m0);
                 }
             }
         }
@@ -185,11 +195,13 @@ __global__ void __launch_bounds__(kWThreads, 1) gemm_w4a16_kernel(const __grid_c
                     if (!ok) break;
                     tc_fence_after();
                     const uint32_t st = base + s * C::kStageBytes;
-                    const uint64_t adesc = desc_sw128(st), bdesc = desc_sw128(st + C::kABytes);
+                    const uint64_t bdesc = desc_sw128(st + WT * C::kABytes);
 #pragma unroll
                     for (int kb = 0; kb < 4; ++kb) {
                         const uint64_t adv = (uint64_t)(kb * 32 >> 4);            // 16 bf16 = 32 bytes along K
-                        tc_mma_bf16(acc, adesc + adv, bdesc + adv, idesc, (ks > 0 || kb > 0) ? 1u : 0u);
+#pragma unroll
+                        for (int w = 0; w < WT; ++w)                              // weight tile w accumulates into columns [w*BN, (w+1)*BN)
+                            tc_mma_bf16(acc + w * BN, desc_sw128(st + w * C::kABytes) + adv, bdesc + adv, idesc, (ks > 0 || kb > 0) ? 1u : 0u);
                     }
                     tc_commit(empty_bar(s));
                 }
@@ -201,33 +213,52 @@ __global__ void __launch_bounds__(kWThreads, 1) gemm_w4a16_kernel(const __grid_c
         // ------------------------------------------------------------------ weight decoders: packed codes + scales -> bf16 tile
         const int t = (warp - 2) * 32 + lane;          // 0..255
         const int row = t >> 1, half = t & 1;          // which weight row of the tile, which 32-element block of the stage
-        uint32_t it = 0;
+        const int block_shift = p.block == 16 ? 4 : (p.block == 32 ? 5 : 6);
+        // Codes and scales are requested kAhead stages before they are decoded (a ring in registers): one stage of
+        // decoding is far shorter than the latency of these 16-byte loads with a row pitch of K/2 bytes.
+        constexpr int kAhead = 4;
+        WBlock ring[kAhead][WT];
+        int pu = blockIdx.x, pks = 0;                  // unit and stage the next request is for
+        int prow0 = pu < total_units ? (pu % p.n_supers) * WT * kTileW + row : p.N;      // this thread's row in that unit's first weight tile
+        auto request = [&](WBlock (&dst)[WT]) {
+#pragma unroll
+            for (int w = 0; w < WT; ++w) dst[w] = load_wblock(p, block_shift, prow0 < p.N ? prow0 + w * kTileW : p.N, pks * kWStageK + half * 32);
+            if (++pks == p.kstages) {
+                pks = 0;
+                pu += gridDim.x;
+                prow0 = pu < total_units ? (pu % p.n_supers) * WT * kTileW + row : p.N;
+            }
+        };
+#pragma unroll
+        for (int j = 0; j < kAhead; ++j) request(ring[j]);
+        const int my_units = blockIdx.x < total_units ? (total_units - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
+        const uint32_t my_stages = (uint32_t)my_units * (uint32_t)p.kstages;
         bool ok = true;
-        WBlock cur = {};
-        if (blockIdx.x < total_units) cur = load_wblock(p, (blockIdx.x % p.n_tiles) * kTileW + row, half * 32);
-        for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x) {
-            for (int ks = 0; ks < p.kstages; ++ks, ++it) {
-                // the next stage's codes and scales are requested before this one is decoded
-                int nu = u, nks = ks + 1;
-                if (nks == p.kstages) { nks = 0; nu = u + gridDim.x; }
-                WBlock nxt = {};
-                if (nu < total_units) nxt = load_wblock(p, (nu % p.n_tiles) * kTileW + row, nks * kWStageK + half * 32);
+        for (uint32_t it0 = 0; it0 < my_stages && ok; it0 += kAhead) {
+#pragma unroll
+            for (int j = 0; j < kAhead; ++j) {
+                const uint32_t it = it0 + j;
+                if (it >= my_stages) break;
                 const int s = it % C::kStages;
                 const uint32_t ph = (it / C::kStages) & 1;
                 ok = __all_sync(0xFFFFFFFFu, mbar_wait(empty_bar(s), ph ^ 1u, abort_flag));
                 if (!ok) break;
-                uint8_t* tile = base_ptr + s * C::kStageBytes;
-                const uint32_t w[4] = {cur.codes.x, cur.codes.y, cur.codes.z, cur.codes.w};
 #pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    // 16-byte chunk index within the 128-byte row, swizzled with the row's position in its group of eight
-                    const int chunk = half * 4 + j;
-                    *reinterpret_cast<uint4*>(tile + row * 128 + ((chunk ^ (row & 7)) << 4)) = decode8(w[j], j < 2 ? cur.s0 : cur.s1);
+                for (int w = 0; w < WT; ++w) {
+                    uint8_t* tile = base_ptr + s * C::kStageBytes + w * C::kABytes;
+                    const WBlock& blk = ring[j][w];
+                    const uint32_t cw[4] = {blk.codes.x, blk.codes.y, blk.codes.z, blk.codes.w};
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        // 16-byte chunk index within the 128-byte row, swizzled with the row's position in its group of eight
+                        const int chunk = half * 4 + c;
+                        *reinterpret_cast<uint4*>(tile + row * 128 + ((chunk ^ (row & 7)) << 4)) = decode8(cw[c], c < 2 ? blk.s0 : blk.s1);
+                    }
                 }
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");       // visible to the tensor core's reads
                 __syncwarp();
                 if (lane == 0) mbar_arrive(w_ready_bar(s));
-                cur = nxt;
+                request(ring[j]);                       // the slot just decoded takes the stage kAhead further on
             }
         }
     } else {
@@ -243,20 +274,22 @@ __global__ void __launch_bounds__(kWThreads, 1) gemm_w4a16_kernel(const __grid_c
             ok = __all_sync(0xFFFFFFFFu, ok && !*abort_flag);
             if (!ok) break;
             tc_fence_after();
-            const int n0 = (u % p.n_tiles) * kTileW + q * 32;
-            const int mt = (u / p.n_tiles) * BN;
-            const int n = n0 + lane;
-            const float bias = (has_bias && n < p.N) ? __bfloat162float(p.bias[n]) : 0.0f;
+            const int mt = (u / p.n_supers) * BN;
 #pragma unroll 1
-            for (int c0 = 0; c0 < BN; c0 += 32) {
+            for (int cc = 0; cc < WT * BN; cc += 32) {
+                const int w = cc / BN, c0 = cc - w * BN;          // weight tile and column inside its accumulator
+                const int n0 = ((u % p.n_supers) * WT + w) * kTileW + q * 32;
+                const int n = n0 + lane;
+                const float bias = (has_bias && n < p.N) ? __bfloat162float(p.bias[n]) : 0.0f;
                 const int m0 = mt + c0;
-                if (m0 >= p.M) {
-                    if (c0 == 0) { tc_fence_before(); __syncwarp(); if (lane == 0) mbar_arrive(acc_empty_bar(buf)); }
-                    break;
+                const bool last = cc + 32 >= WT * BN;             // last read of this accumulator: hand it back
+                if (m0 >= p.M) {                                   // activation rows past M: nothing to store
+                    if (last) { tc_fence_before(); __syncwarp(); if (lane == 0) mbar_arrive(acc_empty_bar(buf)); }
+                    continue;
                 }
                 uint32_t v[32];
-                tc_ld_32x32(tmem + buf * C::kAccStride + ((uint32_t)(q * 32) << 16) + c0, v);
-                if (c0 + 32 >= BN || m0 + 32 >= p.M) {            // last read of this accumulator: hand it back
+                tc_ld_32x32(tmem + buf * C::kAccStride + ((uint32_t)(q * 32) << 16) + cc, v);
+                if (last) {
                     tc_fence_before();
                     __syncwarp();
                     if (lane == 0) mbar_arrive(acc_empty_bar(buf));
@@ -329,21 +362,22 @@ int make_x_map(CUtensorMap* map, const void* ptr, int64_t rows, int64_t cols, in
     return MXFP4_OK;
 }
 
-template <int BN>
+template <int BN, int WT>
 int launch_w4a16(const CUtensorMap& mx, W4A16Params& p, cudaStream_t st) {
-    using C = WCfg<BN>;
+    using C = WCfg<BN, WT>;
     static std::atomic<bool> configured[64];
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev >= 0 && dev < 64 && !configured[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_w4a16_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
+        cudaError_t e = cudaFuncSetAttribute(gemm_w4a16_kernel<BN, WT>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
         if (e != cudaSuccess) return cuda_fail(e, "mxfp4_gemm_w4a16: cudaFuncSetAttribute");
         configured[dev] = true;
     }
     p.m_tiles = (p.M + BN - 1) / BN;
-    const int64_t units = (int64_t)p.n_tiles * p.m_tiles;
+    p.n_supers = (p.n_tiles + WT - 1) / WT;
+    const int64_t units = (int64_t)p.n_supers * p.m_tiles;
     const int grid = (int)(units < num_sms() ? units : num_sms());
-    gemm_w4a16_kernel<BN><<<grid, kWThreads, C::kSmemBytes, st>>>(mx, p);
+    gemm_w4a16_kernel<BN, WT><<<grid, kWThreads, C::kSmemBytes, st>>>(mx, p);
     MXFP4_CHECK_LAUNCH("mxfp4_gemm_w4a16");
     return MXFP4_OK;
 }
@@ -372,7 +406,7 @@ extern "C" int mxfp4_gemm_w4a16(const void* x_bf16, int64_t ldx, const uint8_t* 
     p.bias = (const __nv_bfloat16*)bias_bf16; p.out = (__nv_bfloat16*)out_bf16; p.ldo = ldo;
     p.M = (int)M; p.N = (int)N; p.K = (int)K;
     p.kstages = (int)((K + kWStageK - 1) / kWStageK);
-    p.n_tiles = (int)((N + kTileW - 1) / kTileW); p.m_tiles = 0;
+    p.n_tiles = (int)((N + kTileW - 1) / kTileW); p.m_tiles = 0; p.n_supers = 0;
     p.status = status_dev;
     const int bn = M <= 32 ? 32 : (M <= 64 ? 64 : (M <= 128 ? 128 : 256));
     CUtensorMap mx;
@@ -380,9 +414,9 @@ extern "C" int mxfp4_gemm_w4a16(const void* x_bf16, int64_t ldx, const uint8_t* 
     if (rc) return rc;
     cudaStream_t st = (cudaStream_t)stream;
     switch (bn) {
-        case 32: return launch_w4a16<32>(mx, p, st);
-        case 64: return launch_w4a16<64>(mx, p, st);
-        case 128: return launch_w4a16<128>(mx, p, st);
-        default: return launch_w4a16<256>(mx, p, st);
+        case 32: return launch_w4a16<32, 1>(mx, p, st);
+        case 64: return launch_w4a16<64, 1>(mx, p, st);
+        case 128: return launch_w4a16<128, 1>(mx, p, st);
+        default: return launch_w4a16<256, 1>(mx, p, st);
     }
 }

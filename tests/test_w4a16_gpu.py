@@ -78,3 +78,31 @@ def test_bf16_scale_mxlinear_forward():
     y = quant_matmul(x.cuda(), op.cuda(), os_.cuda())
     ref = (x.float() @ oracle.dequantize(op, os_).to(torch.bfloat16).float().T)
     assert rel_fro(y.float().cpu(), ref) < 5e-3
+
+
+@pytest.mark.parametrize("M", [256, 128, 8])         # 256-, 128- and 32-row activation tiles
+@pytest.mark.parametrize("fmt,block", [("e8m0", 32), ("bf16", 32), ("bf16", 16), ("e8m0", 64)])
+def test_decoded_weights_are_bit_exact(M, fmt, block):
+    """With one-hot activation rows the output IS the kernel's decoded weight matrix: every code under scales from the
+    whole normal range (E8M0 bytes 8..240; bf16 scales with all eight significant bits in use) must equal the reference's
+    dequantize() cast to bf16, bit for bit."""
+    from mxfp4 import gemm
+    N, K = 384, 256
+    g = torch.Generator().manual_seed(17 * block + M)
+    packed = torch.randint(0, 256, (N, K // 2), generator=g, dtype=torch.uint8)
+    packed[0, :8] = torch.arange(0, 256, 32, dtype=torch.uint8) + torch.arange(8, dtype=torch.uint8)      # every code at least once
+    packed[1, :8] = torch.tensor([0x01, 0x23, 0x45, 0x67, 0x89, 0xAB, 0xCD, 0xEF], dtype=torch.uint8)
+    if fmt == "e8m0":
+        scales = torch.randint(8, 241, (N, K // block), generator=g, dtype=torch.uint8)
+    else:
+        mant = torch.randint(0, 128, (N, K // block), generator=g, dtype=torch.int32)
+        expo = torch.randint(90, 150, (N, K // block), generator=g, dtype=torch.int32)
+        scales = ((expo << 7) | mant).to(torch.int16).view(torch.bfloat16)
+    ref = oracle.dequantize(packed, scales, block).to(torch.bfloat16)           # [N, K]
+    x = torch.zeros(M, K, dtype=torch.bfloat16)
+    cols = torch.randperm(K, generator=g)[:M]
+    x[torch.arange(M), cols] = 1.0
+    y = gemm.matmul_w4a16(x.cuda(), packed.cuda(), scales.cuda(), None, block).cpu()
+    gemm.check_status()
+    want = ref[:, cols].T.contiguous()
+    assert torch.equal(y.view(torch.int16), want.view(torch.int16))
