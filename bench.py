@@ -589,7 +589,8 @@ def extra_tp_stack(rank, world, local, n_layers=32):
 
 
 def run_gemm_sweep(args, local):
-    """Kernel-only times of mxfp4_gemm_prequantized over a grid of shapes (current MXFP4_GEMM_MODE / MXFP4_GEMM_PAIR settings)."""
+    """Kernel-only times over a grid of shapes: mxfp4_gemm_prequantized in the FP4 modes, mxfp4_gemm_w4a16 in w4a16 mode
+    (current MXFP4_GEMM_MODE / MXFP4_GEMM_PAIR settings)."""
     import mxfp4
     from mxfp4 import _capi, gemm
     dev = torch.device("cuda", local)
@@ -613,6 +614,9 @@ def run_gemm_sweep(args, local):
             sp = torch.cuda.current_stream(dev).cuda_stream
 
             def kern():
+                if gemm.get_gemm_mode() == "w4a16":
+                    gemm.matmul_w4a16(x, packed, scales, None, 32, out=out)
+                    return
                 rc = L.mxfp4_gemm_prequantized(aq[0].data_ptr(), aq[1].data_ptr(), packed.data_ptr(), prep.data_ptr(), None, out.data_ptr(),
                                                N, M, N, K, mode, spl.data_ptr(), nsp, st.data_ptr(), sp)
                 assert rc == 0, _capi.last_error()
@@ -626,6 +630,7 @@ def run_gemm_sweep(args, local):
             e1.record()
             torch.cuda.synchronize()
             assert int(st[0].item()) == 0, "GEMM kernel reported a timed-out wait"
+            gemm.check_status()
             us = e0.elapsed_time(e1) / 10 * 1e3
             rows.append({"M": M, "N": N, "K": K, "kernel_us": round(us, 1), "tflops": round(2.0 * M * N * K / us / 1e6, 0)})
     return {"sweep": rows, "mode": gemm.get_gemm_mode(), "pair": os.environ.get("MXFP4_GEMM_PAIR", "default")}

@@ -9,36 +9,44 @@
 //     they cannot feed the block-scaled FP4 tensor cores;
 //   * E8M0 weights when the caller wants the reference's literal numerics (no activation quantisation) at the price of
 //     the bf16 tensor rate (a quarter of the FP4 rate).
-// The weight never exists in dequantised form in global memory: eight transform warps read the packed codes and scales
-// straight from global memory (one 32-element block per thread and K stage, the next stage's loads in flight while the
-// current one is decoded), build the bf16 tile in shared memory in the 128-byte-swizzled layout the tensor core reads, and
-// hand it to the MMA thread through an mbarrier.  Activations arrive by TMA.  Accumulators are double-buffered in tensor
-// memory (no scale factors live there for kind::f16), so the epilogue of a tile overlaps the next tile's MMAs.
-// Tile: WT x 128 weight rows (MMA M = 128 each) x BN activation rows (MMA N) x 64 elements of K per stage (one 128-byte
-// swizzle span of bf16), 4 x WT MMAs of K = 16 per stage.  Persistent grid, one CTA per SM.  Every wait is bounded as in the FP4 kernels.
+// The weight never exists in dequantised form in global memory: two groups of eight decoder warps take alternate K
+// stages, so that one group's waits (copies, barriers, the proxy fence) overlap the other's arithmetic.  A thread fetches
+// the packed codes and scales of its (row, 32-element block) with cp.async into a private ring in shared memory, kAhead
+// of its group's stages ahead, builds its part of the bf16 tile in shared memory in the 128-byte-swizzled layout the
+// tensor core reads (integer assembly of the levels, one bf16x2 multiply by the scale), and the group hands the tile to
+// the MMA thread through an mbarrier.  Activations arrive by TMA.  Accumulators are double-buffered in tensor memory (no
+// scale factors live there for kind::f16), so the epilogue of a tile overlaps the next tile's MMAs.
+// Tile: 128 weight rows (MMA M) x BN activation rows (MMA N) x 64 elements of K per stage (one 128-byte swizzle span of
+// bf16), 4 MMAs of K = 16 per stage.  Persistent grid, one CTA per SM.  Every wait is bounded as in the FP4 kernels.
 #include <atomic>
 #include "gemm_mxf4_tc.cuh"
 
 namespace mxfp4 {
 namespace {
 
-constexpr int kWThreads = 448;      // warps: 0 TMA producer, 1 MMA issuer (owns tensor memory), 2-9 weight decoders, 10-13 epilogue
+constexpr int kWThreads = 704;      // warps: 0 TMA producer, 1 MMA issuer (owns tensor memory), 2-17 weight decoders, 18-21 epilogue
 constexpr int kWStageK = 64;        // elements of K per stage
 
-// WT weight tiles of 128 rows share one activation tile.  Only WT = 1 is instantiated: two weight tiles against a
-// 128-row activation tile need a third less L2 traffic than one against 256 rows, but measured 527 against 891 TFLOP/s
-// on [8192, 11008, 4096] (MMAs of 128 columns read their operands from shared memory at twice the rate per flop).
-template <int BN, int WT>
+constexpr int kGroups = 2;          // decoder groups: group g decodes the K stages with index = g (mod kGroups)
+constexpr int kGroupThreads = 256;  // per group: (weight row of the tile, which 32-element block of the stage)
+constexpr int kDecoders = kGroups * kGroupThreads;
+constexpr int kAhead = 2;           // stages OF ITS GROUP between a thread's request for its scales and their use
+
+// (Two 128-row weight tiles against one 128-row activation tile would need a third less L2 traffic than 128 x 256, but
+// measured 527 against 891 TFLOP/s on [8192, 11008, 4096]: MMAs of 128 columns read their operands from shared memory at
+// twice the rate per flop.)
+template <int BN>
 struct WCfg {
-    static constexpr int kABytes = kTileW * 128;                 // one decoded weight tile: 128 rows x 64 bf16
+    static constexpr int kABytes = kTileW * 128;                 // decoded weight tile: 128 rows x 64 bf16
     static constexpr int kBBytes = BN * 128;                     // activation tile: BN rows x 64 bf16
-    static constexpr int kStageBytes = WT * kABytes + kBBytes;
-    static constexpr int kEpiBytes = 4 * 4096;
-    static constexpr int kBudget = 227 * 1024 - 1024 - 512 - kEpiBytes;
+    static constexpr int kCBytes = kTileW * (kWStageK / 2);      // packed codes of the weight tile: 128 rows x 32 bytes
+    static constexpr int kStageBytes = kABytes + kBBytes + kCBytes;
+    static constexpr int kFetchBytes = kAhead * kDecoders * 8;   // per thread and stage in flight: two words of scales
+    static constexpr int kBudget = 227 * 1024 - 1024 - 512 - kFetchBytes;
     static constexpr int kStages = (kBudget / kStageBytes) < 6 ? (kBudget / kStageBytes) : 6;
-    static constexpr int kSmemBytes = kStages * kStageBytes + kEpiBytes + 1024 + 512;
+    static constexpr int kSmemBytes = kStages * kStageBytes + kFetchBytes + 1024 + 512;
     static constexpr int kAccStride = 256;                       // two accumulators of up to 256 columns
-    static_assert(BN % 32 == 0 && WT * BN <= 256 && kStages >= 2 && kStageBytes % 1024 == 0, "tile width");
+    static_assert(BN % 32 == 0 && BN <= 256 && kStages >= 2 && kStageBytes % 1024 == 0, "tile width");
 };
 
 struct W4A16Params {
@@ -49,7 +57,7 @@ struct W4A16Params {
     __nv_bfloat16* out;
     int64_t ldo;
     int M, N, K;
-    int kstages, n_tiles, n_supers, m_tiles;      // n_supers: groups of WT weight tiles
+    int kstages, n_tiles, m_tiles;
     int* status;
 };
 
@@ -67,32 +75,22 @@ __device__ __forceinline__ void tc_mma_bf16(uint32_t d_tmem, uint64_t adesc, uin
         : "memory");
 }
 
-// what one decoder thread needs for one (row, 32-element block) of a stage
-struct WBlock {
-    uint4 codes;               // 16 bytes = 32 codes
-    __nv_bfloat162 s0, s1;     // scale of elements 0-15 and 16-31 in both halves (they differ only for block_size 16)
-};
-
-// A scale as a bf16 pair.  Exact: a bf16 scale is taken as it is, 2^(byte-127) is a bf16 value for every byte (a
-// subnormal one for byte 0).
-__device__ __forceinline__ __nv_bfloat162 scale_pair(const W4A16Params& p, int64_t idx) {
-    if (p.scale_fmt == MXFP4_SF_E8M0) return __float2bfloat162_rn(e8m0_value(__ldg(reinterpret_cast<const uint8_t*>(p.w_scales) + idx)));
-    return __bfloat162bfloat162(__ldg(reinterpret_cast<const __nv_bfloat16*>(p.w_scales) + idx));
+// A scale as a bf16 pair from its stored form (the E8M0 byte or the bf16 bit pattern).  Exact: a bf16 scale is taken as
+// it is, 2^(byte-127) is a bf16 value for every byte (a subnormal one for byte 0, +inf for byte 255, as the reference's
+// float32 scale cast to bf16 would be).
+__device__ __forceinline__ __nv_bfloat162 scale_pair(int scale_fmt, uint32_t raw) {
+    uint32_t bits = raw;
+    if (scale_fmt == MXFP4_SF_E8M0) bits = raw == 0 ? 0x0040u : raw << 7;
+    bits |= bits << 16;
+    return *reinterpret_cast<const __nv_bfloat162*>(&bits);
 }
 
-// k0: first element of the block, a multiple of 32; block_shift = log2(block size)
-__device__ __forceinline__ WBlock load_wblock(const W4A16Params& p, int block_shift, int n, int k0) {
-    WBlock b;
-    b.codes = make_uint4(0, 0, 0, 0);
-    b.s0 = b.s1 = __float2bfloat162_rn(0.0f);             // rows past N and blocks past K decode to zero
-    if (n < p.N && k0 < p.K) {
-        b.codes = __ldg(reinterpret_cast<const uint4*>(p.w_packed + (int64_t)n * (p.K >> 1) + (k0 >> 1)));
-        const int64_t first = (int64_t)n * (p.K >> block_shift) + (k0 >> block_shift);
-        b.s0 = scale_pair(p, first);
-        b.s1 = block_shift == 4 ? scale_pair(p, first + 1) : b.s0;
-    }
-    return b;
+__device__ __forceinline__ void cp_async_4(uint32_t dst, const void* src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(src) : "memory");
 }
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int kPending>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(kPending) : "memory"); }
 
 // Four code bytes (8 elements, even element in the high nibble) -> four bf16 pairs: bf16(level * scale), as the
 // reference's dequantize() followed by the cast to the activations' dtype gives them.  The level of a code c = e<<1 | m
@@ -114,31 +112,32 @@ __device__ __forceinline__ uint4 decode8(uint32_t w, __nv_bfloat162 s2) {
     return make_uint4(__byte_perm(r04, r15, 0x5410), __byte_perm(r26, r37, 0x5410), __byte_perm(r04, r15, 0x7632), __byte_perm(r26, r37, 0x7632));
 }
 
-template <int BN, int WT>
-__global__ void __launch_bounds__(kWThreads, 1) gemm_w4a16_kernel(const __grid_constant__ CUtensorMap map_x, const W4A16Params p) {
-    using C = WCfg<BN, WT>;
+template <int BN>
+__global__ void __launch_bounds__(kWThreads, 1) gemm_w4a16_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
+                                                                  const W4A16Params p) {
+    using C = WCfg<BN>;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;                 // 128-byte swizzle wants 1024-byte aligned tiles
     uint8_t* base_ptr = smem_raw + (base - raw);
-    uint8_t* epi_ptr = base_ptr + C::kStages * C::kStageBytes;
-    const uint32_t bars = base + C::kStages * C::kStageBytes + C::kEpiBytes;
-    auto x_full_bar = [&](int s) { return bars + 8u * s; };                        // the activation tile has landed (TMA bytes)
-    auto w_ready_bar = [&](int s) { return bars + 8u * (C::kStages + s); };        // the eight decoder warps have written the weight tile
+    const uint32_t fetch = base + C::kStages * C::kStageBytes;    // [kAhead][512] x 8 bytes of scale words
+    const uint32_t bars = fetch + C::kFetchBytes;
+    auto x_full_bar = [&](int s) { return bars + 8u * s; };                        // the activation tile and the packed codes have landed (TMA bytes)
+    auto w_ready_bar = [&](int s) { return bars + 8u * (C::kStages + s); };        // the eight decoder warps of the stage's group have written the weight tile
     auto empty_bar = [&](int s) { return bars + 8u * (2 * C::kStages + s); };      // the MMAs have finished with the stage
     auto acc_full_bar = [&](int b) { return bars + 8u * (3 * C::kStages + b); };
     auto acc_empty_bar = [&](int b) { return bars + 8u * (3 * C::kStages + 2 + b); };
-    uint8_t* tail = epi_ptr + C::kEpiBytes + 8 * (3 * C::kStages + 4);
+    uint8_t* tail = base_ptr + C::kStages * C::kStageBytes + C::kFetchBytes + 8 * (3 * C::kStages + 4);
     volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(tail);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tail + 4);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int total_units = p.n_supers * p.m_tiles;
+    const int total_units = p.n_tiles * p.m_tiles;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < C::kStages; ++s) {
             mbar_init(x_full_bar(s), 1);
-            mbar_init(w_ready_bar(s), 8);
+            mbar_init(w_ready_bar(s), kGroupThreads / 32);
             mbar_init(empty_bar(s), 1);
         }
         for (int b = 0; b < 2; ++b) {
@@ -164,13 +163,14 @@ __global__ void __launch_bounds__(kWThreads, 1) gemm_w4a16_kernel(const __grid_c
             uint32_t it = 0;
             bool ok = true;
             for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x) {
-                const int m0 = (u / p.n_supers) * BN;
+                const int m0 = (u / p.n_tiles) * BN, n0 = (u % p.n_tiles) * kTileW;
                 for (int ks = 0; ks < p.kstages; ++ks, ++it) {
                     const int s = it % C::kStages;
                     const uint32_t ph = (it / C::kStages) & 1;
                     if (!mbar_wait(empty_bar(s), ph ^ 1u, abort_flag)) { ok = false; break; }
-                    mbar_expect_tx(x_full_bar(s), C::kBBytes);
-                    tma_load_2d(base + s * C::kStageBytes + WT * C::kABytes, &map_x, x_full_bar(s), ks * kWStageK, m0);
+                    mbar_expect_tx(x_full_bar(s), C::kBBytes + C::kCBytes);
+                    tma_load_2d(base + s * C::kStageBytes + C::kABytes + C::kBBytes, &map_w, x_full_bar(s), ks * (kWStageK / 2), n0);
+                    tma_load_2d(base + s * C::kStageBytes + C::kABytes, &map_x, x_full_bar(s), ks * kWStageK, m0);
                 }
             }
         }
@@ -195,13 +195,11 @@ __global__ void __launch_bounds__(kWThreads, 1) gemm_w4a16_kernel(const __grid_c
                     if (!ok) break;
                     tc_fence_after();
                     const uint32_t st = base + s * C::kStageBytes;
-                    const uint64_t bdesc = desc_sw128(st + WT * C::kABytes);
+                    const uint64_t adesc = desc_sw128(st), bdesc = desc_sw128(st + C::kABytes);
 #pragma unroll
                     for (int kb = 0; kb < 4; ++kb) {
                         const uint64_t adv = (uint64_t)(kb * 32 >> 4);            // 16 bf16 = 32 bytes along K
-#pragma unroll
-                        for (int w = 0; w < WT; ++w)                              // weight tile w accumulates into columns [w*BN, (w+1)*BN)
-                            tc_mma_bf16(acc + w * BN, desc_sw128(st + w * C::kABytes) + adv, bdesc + adv, idesc, (ks > 0 || kb > 0) ? 1u : 0u);
+                        tc_mma_bf16(acc, adesc + adv, bdesc + adv, idesc, (ks > 0 || kb > 0) ? 1u : 0u);
                     }
                     tc_commit(empty_bar(s));
                 }
@@ -209,62 +207,105 @@ __global__ void __launch_bounds__(kWThreads, 1) gemm_w4a16_kernel(const __grid_c
             }
         }
         __syncwarp();
-    } else if (warp < 10) {
+    } else if (warp < 2 + kDecoders / 32) {
         // ------------------------------------------------------------------ weight decoders: packed codes + scales -> bf16 tile
-        const int t = (warp - 2) * 32 + lane;          // 0..255
-        const int row = t >> 1, half = t & 1;          // which weight row of the tile, which 32-element block of the stage
+        const int group = (warp - 2) / (kGroupThreads / 32);
+        const int t = (warp - 2) * 32 + lane;                                      // 0..511: slot in the fetch rings
+        const int tg = t - group * kGroupThreads;
+        const int row = tg >> 1, half = tg & 1;        // which weight row of the tile, which 32-element block of the stage
         const int block_shift = p.block == 16 ? 4 : (p.block == 32 ? 5 : 6);
-        // Codes and scales are requested kAhead stages before they are decoded (a ring in registers): one stage of
-        // decoding is far shorter than the latency of these 16-byte loads with a row pitch of K/2 bytes.
-        constexpr int kAhead = 4;
-        WBlock ring[kAhead][WT];
-        int pu = blockIdx.x, pks = 0;                  // unit and stage the next request is for
-        int prow0 = pu < total_units ? (pu % p.n_supers) * WT * kTileW + row : p.N;      // this thread's row in that unit's first weight tile
-        auto request = [&](WBlock (&dst)[WT]) {
-#pragma unroll
-            for (int w = 0; w < WT; ++w) dst[w] = load_wblock(p, block_shift, prow0 < p.N ? prow0 + w * kTileW : p.N, pks * kWStageK + half * 32);
-            if (++pks == p.kstages) {
-                pks = 0;
-                pu += gridDim.x;
-                prow0 = pu < total_units ? (pu % p.n_supers) * WT * kTileW + row : p.N;
+        const int sbytes = p.scale_fmt == MXFP4_SF_E8M0 ? 1 : 2;
+        const int slen = (block_shift == 4 ? 2 : 1) * sbytes;                      // bytes of scales per thread and stage: 1, 2 or 4
+        const uint32_t scale_ring = fetch + (uint32_t)t * 8u;
+        auto scale_slot = [&](int j) { return scale_ring + (uint32_t)(j * kDecoders * 8); };
+        // weight row of unit u this thread decodes, p.N (outside) when the CTA has no such unit
+        auto unit_row = [&](int u) { return u < total_units ? (u % p.n_tiles) * kTileW + row : p.N; };
+        // byte offset of the first scale of element k0 within the row's scales
+        auto scale_off = [&](int k0) { return (uint32_t)((k0 >> block_shift) * sbytes); };
+        const uintptr_t sbase = reinterpret_cast<uintptr_t>(p.w_scales);
+        const int64_t srow = (int64_t)(p.K >> block_shift) * sbytes;              // bytes of scales per weight row
+
+        // A cursor over this group's stages: (unit, stage of the unit), kGroups stages of the CTA's sequence per step.
+        struct Cursor { int u, ks, row; };
+        auto advance = [&](Cursor& c) {
+            c.ks += kGroups;
+            while (c.ks >= p.kstages && c.u < total_units) {
+                c.ks -= p.kstages;
+                c.u += gridDim.x;
+                c.row = unit_row(c.u);
             }
         };
+        Cursor rq{(int)blockIdx.x, 0, unit_row(blockIdx.x)};       // request cursor, kAhead steps ahead of the decode cursor
+        rq.ks = group - kGroups;
+        advance(rq);
+        Cursor dc = rq;                                             // decode cursor
+        // The packed codes of a stage arrive by TMA with the activations; a thread fetches its own scales with cp.async,
+        // kAhead steps ahead.  One copy group per step, empty for blocks outside the matrix, so that "all but the newest
+        // kAhead-1 groups are complete" always means "the scales of the stage to decode are here".
+        auto request = [&](int j) {
+            const int k0 = rq.ks * kWStageK + half * 32;
+            if (rq.row < p.N && k0 < p.K) {
+                // the aligned word holding the first scale byte, and the next one only where the bytes run into it
+                const uintptr_t a = sbase + (uintptr_t)(rq.row * srow) + scale_off(k0), a0 = a & ~(uintptr_t)3;
+                cp_async_4(scale_slot(j), reinterpret_cast<const void*>(a0));
+                if ((a & 3) + slen > 4) cp_async_4(scale_slot(j) + 4, reinterpret_cast<const void*>(a0 + 4));
+            }
+            cp_async_commit();
+            advance(rq);
+        };
 #pragma unroll
-        for (int j = 0; j < kAhead; ++j) request(ring[j]);
+        for (int j = 0; j < kAhead; ++j) request(j);
+
         const int my_units = blockIdx.x < total_units ? (total_units - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
-        const uint32_t my_stages = (uint32_t)my_units * (uint32_t)p.kstages;
+        const uint32_t my_stages = (uint32_t)my_units * (uint32_t)p.kstages;       // of the whole CTA; this group takes every kGroups-th
         bool ok = true;
-        for (uint32_t it0 = 0; it0 < my_stages && ok; it0 += kAhead) {
+        for (uint32_t it0 = group; it0 < my_stages && ok; it0 += kGroups * kAhead) {
 #pragma unroll
             for (int j = 0; j < kAhead; ++j) {
-                const uint32_t it = it0 + j;
+                const uint32_t it = it0 + j * kGroups;
                 if (it >= my_stages) break;
+                cp_async_wait<kAhead - 1>();
+                const int k0 = dc.ks * kWStageK + half * 32;
+                const bool valid = dc.row < p.N && k0 < p.K;        // rows past N and blocks past K decode to zero
+                uint32_t raw0 = 0, raw1 = 0;
+                if (valid) {
+                    uint32_t w0, w1;
+                    asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(w0), "=r"(w1) : "r"(scale_slot(j)) : "memory");
+                    const uint32_t a_lo = (uint32_t)(sbase + (uintptr_t)(dc.row * srow)) + scale_off(k0);
+                    // this thread's scale bytes, first one lowest (w1 is only meaningful where the bytes run into it)
+                    const uint32_t v = __funnelshift_r(w0, w1, (a_lo & 3u) * 8u);
+                    raw0 = sbytes == 1 ? (v & 0xFFu) : (v & 0xFFFFu);
+                    raw1 = block_shift != 4 ? raw0 : (sbytes == 1 ? ((v >> 8) & 0xFFu) : (v >> 16));
+                }
+                __nv_bfloat162 s0 = scale_pair(p.scale_fmt, raw0), s1 = scale_pair(p.scale_fmt, raw1);
+                if (!valid) s0 = s1 = __float2bfloat162_rn(0.0f);
+                advance(dc);
                 const int s = it % C::kStages;
                 const uint32_t ph = (it / C::kStages) & 1;
-                ok = __all_sync(0xFFFFFFFFu, mbar_wait(empty_bar(s), ph ^ 1u, abort_flag));
+                // the stage's TMA loads are issued only after its previous MMAs have finished (the producer waits for
+                // that), so once the codes are here the decoded tile may be overwritten too
+                ok = __all_sync(0xFFFFFFFFu, mbar_wait(x_full_bar(s), ph, abort_flag));
                 if (!ok) break;
+                uint4 codes;        // [128 rows][32 bytes], as the TMA wrote them (rows past N and bytes past K/2 are zero)
+                asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(codes.x), "=r"(codes.y), "=r"(codes.z), "=r"(codes.w)
+                             : "r"(base + s * C::kStageBytes + C::kABytes + C::kBBytes + tg * 16) : "memory");
+                uint8_t* dst = base_ptr + s * C::kStageBytes + row * 128;
+                const uint32_t cw[4] = {codes.x, codes.y, codes.z, codes.w};
 #pragma unroll
-                for (int w = 0; w < WT; ++w) {
-                    uint8_t* tile = base_ptr + s * C::kStageBytes + w * C::kABytes;
-                    const WBlock& blk = ring[j][w];
-                    const uint32_t cw[4] = {blk.codes.x, blk.codes.y, blk.codes.z, blk.codes.w};
-#pragma unroll
-                    for (int c = 0; c < 4; ++c) {
-                        // 16-byte chunk index within the 128-byte row, swizzled with the row's position in its group of eight
-                        const int chunk = half * 4 + c;
-                        *reinterpret_cast<uint4*>(tile + row * 128 + ((chunk ^ (row & 7)) << 4)) = decode8(cw[c], c < 2 ? blk.s0 : blk.s1);
-                    }
-                }
+                for (int c = 0; c < 4; ++c)     // 16-byte chunk index within the 128-byte row, swizzled with the row's position in its group of eight
+                    *reinterpret_cast<uint4*>(dst + (((half * 4 + c) ^ (row & 7)) << 4)) = decode8(cw[c], c < 2 ? s0 : s1);
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");       // visible to the tensor core's reads
                 __syncwarp();
                 if (lane == 0) mbar_arrive(w_ready_bar(s));
-                request(ring[j]);                       // the slot just decoded takes the stage kAhead further on
+                request(j);                             // the scale slot just read takes the step kAhead further on
             }
         }
+        cp_async_wait<0>();
     } else {
         // ------------------------------------------------------------------ epilogue
+        // A thread holds weight row n (its lane of tensor memory) for 32 activation rows: out[m][n0 + lane] makes every
+        // store of a warp one 64-byte run.
         const int q = warp & 3;                               // tensor-memory lane quarter this warp may read
-        uint32_t* tile = reinterpret_cast<uint32_t*>(epi_ptr + (warp - 10) * 4096);
         const bool has_bias = p.bias != nullptr;
         int i = 0;
         bool ok = true;
@@ -274,49 +315,34 @@ __global__ void __launch_bounds__(kWThreads, 1) gemm_w4a16_kernel(const __grid_c
             ok = __all_sync(0xFFFFFFFFu, ok && !*abort_flag);
             if (!ok) break;
             tc_fence_after();
-            const int mt = (u / p.n_supers) * BN;
+            const int n = (u % p.n_tiles) * kTileW + q * 32 + lane;
+            const int mt = (u / p.n_tiles) * BN;
+            const float bias = (has_bias && n < p.N) ? __bfloat162float(p.bias[n]) : 0.0f;
 #pragma unroll 1
-            for (int cc = 0; cc < WT * BN; cc += 32) {
-                const int w = cc / BN, c0 = cc - w * BN;          // weight tile and column inside its accumulator
-                const int n0 = ((u % p.n_supers) * WT + w) * kTileW + q * 32;
-                const int n = n0 + lane;
-                const float bias = (has_bias && n < p.N) ? __bfloat162float(p.bias[n]) : 0.0f;
+            for (int c0 = 0; c0 < BN; c0 += 32) {
                 const int m0 = mt + c0;
-                const bool last = cc + 32 >= WT * BN;             // last read of this accumulator: hand it back
-                if (m0 >= p.M) {                                   // activation rows past M: nothing to store
-                    if (last) { tc_fence_before(); __syncwarp(); if (lane == 0) mbar_arrive(acc_empty_bar(buf)); }
-                    continue;
+                if (m0 >= p.M) {
+                    if (c0 == 0) { tc_fence_before(); __syncwarp(); if (lane == 0) mbar_arrive(acc_empty_bar(buf)); }
+                    break;
                 }
                 uint32_t v[32];
-                tc_ld_32x32(tmem + buf * C::kAccStride + ((uint32_t)(q * 32) << 16) + cc, v);
-                if (last) {
+                tc_ld_32x32(tmem + buf * C::kAccStride + ((uint32_t)(q * 32) << 16) + c0, v);
+                if (c0 + 32 >= BN || m0 + 32 >= p.M) {            // last read of this accumulator: hand it back
                     tc_fence_before();
                     __syncwarp();
                     if (lane == 0) mbar_arrive(acc_empty_bar(buf));
                 }
-                __nv_bfloat16* t16 = reinterpret_cast<__nv_bfloat16*>(tile);
+                if (n < p.N) {
+                    __nv_bfloat16* o = p.out + (int64_t)m0 * p.ldo + n;
 #pragma unroll
-                for (int j = 0; j < 32; ++j) {
-                    __nv_bfloat16 y = __float2bfloat16_rn(__uint_as_float(v[j]));
-                    if (has_bias) y = __float2bfloat16_rn(__bfloat162float(y) + bias);   // `output += bias` in bf16
-                    t16[j * 32 + lane] = y;
-                }
-                __syncwarp();
-                const bool vec = (p.ldo % 8 == 0) && (((uintptr_t)p.out) % 16 == 0) && (n0 + 32 <= p.N);
-#pragma unroll
-                for (int r = 0; r < 4; ++r) {
-                    const int rw = r * 8 + (lane >> 2), seg = lane & 3;
-                    const int m = m0 + rw;
-                    if (m < p.M) {
-                        if (vec) {
-                            *reinterpret_cast<uint4*>(p.out + (int64_t)m * p.ldo + n0 + seg * 8) = *reinterpret_cast<const uint4*>(t16 + rw * 32 + seg * 8);
-                        } else {
-                            for (int e = 0; e < 8; ++e)
-                                if (n0 + seg * 8 + e < p.N) p.out[(int64_t)m * p.ldo + n0 + seg * 8 + e] = t16[rw * 32 + seg * 8 + e];
+                    for (int j = 0; j < 32; ++j) {
+                        if (m0 + j < p.M) {
+                            __nv_bfloat16 y = __float2bfloat16_rn(__uint_as_float(v[j]));
+                            if (has_bias) y = __float2bfloat16_rn(__bfloat162float(y) + bias);   // `output += bias` in bf16
+                            o[(int64_t)j * p.ldo] = y;
                         }
                     }
                 }
-                __syncwarp();
             }
         }
     }
@@ -340,9 +366,7 @@ __global__ void __launch_bounds__(kWThreads, 1) gemm_w4a16_kernel(const __grid_c
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
-// bf16 matrix [rows, cols] with row pitch ld elements, boxes of 64 elements (128 bytes) x box_rows, 128-byte swizzle,
-// out-of-range parts of a box read as zero
-int make_x_map(CUtensorMap* map, const void* ptr, int64_t rows, int64_t cols, int64_t ld, int box_rows) {
+EncodeTiledFn encode_tiled() {
     static std::atomic<EncodeTiledFn> fn{nullptr};
     if (!fn.load()) {
         void* f = nullptr;
@@ -350,7 +374,13 @@ int make_x_map(CUtensorMap* map, const void* ptr, int64_t rows, int64_t cols, in
         if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &qres) == cudaSuccess && qres == cudaDriverEntryPointSuccess)
             fn.store((EncodeTiledFn)f);
     }
-    EncodeTiledFn enc = fn.load();
+    return fn.load();
+}
+
+// bf16 matrix [rows, cols] with row pitch ld elements, boxes of 64 elements (128 bytes) x box_rows, 128-byte swizzle,
+// out-of-range parts of a box read as zero
+int make_x_map(CUtensorMap* map, const void* ptr, int64_t rows, int64_t cols, int64_t ld, int box_rows) {
+    EncodeTiledFn enc = encode_tiled();
     if (!enc) { set_error("cuTensorMapEncodeTiled is not available from this driver"); return MXFP4_E_CUDA; }
     cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
     cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
@@ -362,22 +392,35 @@ int make_x_map(CUtensorMap* map, const void* ptr, int64_t rows, int64_t cols, in
     return MXFP4_OK;
 }
 
-template <int BN, int WT>
-int launch_w4a16(const CUtensorMap& mx, W4A16Params& p, cudaStream_t st) {
-    using C = WCfg<BN, WT>;
+// packed codes [rows, row_bytes] uint8, boxes of 32 bytes (64 codes) x 128 rows, no swizzle, out-of-range parts read as zero
+int make_w_map(CUtensorMap* map, const void* ptr, int64_t rows, int64_t row_bytes) {
+    EncodeTiledFn enc = encode_tiled();
+    if (!enc) { set_error("cuTensorMapEncodeTiled is not available from this driver"); return MXFP4_E_CUDA; }
+    cuuint64_t dims[2] = {(cuuint64_t)row_bytes, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)row_bytes};
+    cuuint32_t box[2] = {(cuuint32_t)(kWStageK / 2), (cuuint32_t)kTileW};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) { set_error("cuTensorMapEncodeTiled (packed codes) failed with CUresult %d", (int)r); return MXFP4_E_CUDA; }
+    return MXFP4_OK;
+}
+
+template <int BN>
+int launch_w4a16(const CUtensorMap& mx, const CUtensorMap& mw, W4A16Params& p, cudaStream_t st) {
+    using C = WCfg<BN>;
     static std::atomic<bool> configured[64];
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev >= 0 && dev < 64 && !configured[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_w4a16_kernel<BN, WT>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
+        cudaError_t e = cudaFuncSetAttribute(gemm_w4a16_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
         if (e != cudaSuccess) return cuda_fail(e, "mxfp4_gemm_w4a16: cudaFuncSetAttribute");
         configured[dev] = true;
     }
     p.m_tiles = (p.M + BN - 1) / BN;
-    p.n_supers = (p.n_tiles + WT - 1) / WT;
-    const int64_t units = (int64_t)p.n_supers * p.m_tiles;
+    const int64_t units = (int64_t)p.n_tiles * p.m_tiles;
     const int grid = (int)(units < num_sms() ? units : num_sms());
-    gemm_w4a16_kernel<BN, WT><<<grid, kWThreads, C::kSmemBytes, st>>>(mx, p);
+    gemm_w4a16_kernel<BN><<<grid, kWThreads, C::kSmemBytes, st>>>(mx, mw, p);
     MXFP4_CHECK_LAUNCH("mxfp4_gemm_w4a16");
     return MXFP4_OK;
 }
@@ -406,17 +449,20 @@ extern "C" int mxfp4_gemm_w4a16(const void* x_bf16, int64_t ldx, const uint8_t* 
     p.bias = (const __nv_bfloat16*)bias_bf16; p.out = (__nv_bfloat16*)out_bf16; p.ldo = ldo;
     p.M = (int)M; p.N = (int)N; p.K = (int)K;
     p.kstages = (int)((K + kWStageK - 1) / kWStageK);
-    p.n_tiles = (int)((N + kTileW - 1) / kTileW); p.m_tiles = 0; p.n_supers = 0;
+    p.n_tiles = (int)((N + kTileW - 1) / kTileW); p.m_tiles = 0;
     p.status = status_dev;
     const int bn = M <= 32 ? 32 : (M <= 64 ? 64 : (M <= 128 ? 128 : 256));
     CUtensorMap mx;
+    CUtensorMap mw;
     int rc = make_x_map(&mx, x_bf16, M, K, ldx, bn);
+    if (rc) return rc;
+    rc = make_w_map(&mw, w_packed, N, K / 2);
     if (rc) return rc;
     cudaStream_t st = (cudaStream_t)stream;
     switch (bn) {
-        case 32: return launch_w4a16<32, 1>(mx, p, st);
-        case 64: return launch_w4a16<64, 1>(mx, p, st);
-        case 128: return launch_w4a16<128, 1>(mx, p, st);
-        default: return launch_w4a16<256, 1>(mx, p, st);
+        case 32: return launch_w4a16<32>(mx, mw, p, st);
+        case 64: return launch_w4a16<64>(mx, mw, p, st);
+        case 128: return launch_w4a16<128>(mx, mw, p, st);
+        default: return launch_w4a16<256>(mx, mw, p, st);
     }
 }

@@ -106,3 +106,23 @@ def test_decoded_weights_are_bit_exact(M, fmt, block):
     gemm.check_status()
     want = ref[:, cols].T.contiguous()
     assert torch.equal(y.view(torch.int16), want.view(torch.int16))
+
+
+@pytest.mark.parametrize("fmt,block,shift", [("e8m0", 16, 1), ("e8m0", 16, 3), ("e8m0", 32, 1), ("bf16", 16, 1), ("bf16", 32, 1)])
+def test_scales_at_any_alignment(fmt, block, shift):
+    """The decoders fetch scales as aligned 4-byte words; a scale tensor that starts `shift` elements into its storage
+    (bytes run across a word boundary) must decode the same."""
+    from mxfp4 import gemm
+    M, N, K = 64, 256, 512
+    w = weight(N, K, 5, True)
+    x = act(M, K, 77)
+    op, os_ = oracle.quantize(w, block, fmt)
+    store = torch.zeros(os_.numel() + 8, dtype=os_.dtype)
+    store[shift:shift + os_.numel()] = os_.reshape(-1)
+    dev_scales = store.cuda()[shift:shift + os_.numel()].view(os_.shape)
+    assert dev_scales.data_ptr() % 4 != 0 and dev_scales.is_contiguous()
+    y = gemm.matmul_w4a16(x.cuda(), op.cuda(), dev_scales, None, block)
+    y0 = gemm.matmul_w4a16(x.cuda(), op.cuda(), os_.cuda(), None, block)
+    gemm.check_status()
+    assert torch.equal(y, y0)
+    assert rel_fro(y.float().cpu(), oracle.matmul_w4a16(x, op, os_, None, block).float()) <= TOL
