@@ -1,7 +1,7 @@
 """The reference's OWN test files, unmodified, against this package (drop-in proof of the API surface).
 
-They are read from a checkout of the reference at test time (MXFP4_REFERENCE_DIR, default /root/reference); nothing of
-them is copied here, and the test is skipped where no checkout exists.  The reference's tests create CPU tensors, and this
+They are read from a checkout of the reference at test time (the directory MXFP4_REFERENCE_DIR names, else REF's default
+below); nothing of them is copied here, and the test is skipped where no checkout exists.  The reference's tests create CPU tensors, and this
 package has no CPU path, so the run happens in a child pytest process in which the CPU oracle stands in for the CUDA
 kernels (tests/ref_plugin.py); what is exercised is this package's Python surface: names, signatures, shapes, dtypes,
 state_dict flow, error behaviour.  tests/test_fused.py and tests/test_dispatcher.py of the reference drive its Triton
