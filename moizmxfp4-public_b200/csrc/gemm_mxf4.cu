@@ -570,8 +570,14 @@ inline int64_t align_up(int64_t v, int64_t a) { return (v + a - 1) / a * a; }
 // Problems with fewer tiles than SMs leave most of the chip idle; narrower tiles or a cut along K spread the weight
 // stream over it.  The model was fitted to the measured grid M in {192..1024} x {4096^2, 11008x4096, 4096x11008} and is
 // within ~10 % of the best measured (bn, ksplit) everywhere there.  MXFP4_GEMM_BN / MXFP4_GEMM_KSPLIT override.
+//
+// swap: the kernel of gemm_mxf4_swap.cu (activations on the MMA's M side, 256 weight rows per tile) instead.  With at
+// most 128 activation rows a 128-row weight tile costs the same MMA time as a 256-row one there, so it is taken where
+// the 128-row tiles need two rounds over the SMs and the 256-row tiles one (e.g. [128, 22016, 4096]: 172 tiles on 148
+// SMs).  MXFP4_GEMM_SWAP=1 takes it for every M <= 128, MXFP4_GEMM_SWAP=0 never.
 struct TilePlan {
     int bn, ksplit;
+    bool swap;
 };
 TilePlan pick_plan(int64_t M, int64_t N, int64_t K) {
     const int64_t nks = (K + kStageK - 1) / kStageK;
@@ -586,9 +592,21 @@ TilePlan pick_plan(int64_t M, int64_t N, int64_t K) {
         const int v = atoi(e);
         if (v >= 1 && v <= 32) force_ks = v <= nks ? v : (int)nks;
     }
+    if (M <= 128) {
+        const int64_t wide = (N + 255) / 256;
+        const char* e = getenv("MXFP4_GEMM_SWAP");
+        const int forced = e ? atoi(e) : -1;
+        if (forced == 1 || (forced < 0 && n_tiles > sms && wide <= sms)) {
+            int64_t ks = force_ks ? force_ks : sms / wide;          // K ranges only while they fit the same round
+            if (ks > 8) ks = 8;
+            if (ks > nks) ks = nks;
+            if (ks < 1) ks = 1;
+            return {256, (int)ks, true};
+        }
+    }
     static const int kWidths[5] = {32, 64, 128, 192, 256};
     static const int kT1000[5] = {700, 800, 1000, 1190, 1375};     // t(bn) x 1000 (narrow tiles: measured, latency-dominated)
-    TilePlan best = {128, 1};
+    TilePlan best = {128, 1, false};
     int64_t best_cost = -1;
     for (int i = 0; i < 5; ++i) {
         const int bn = kWidths[i];
@@ -600,12 +618,11 @@ TilePlan pick_plan(int64_t M, int64_t N, int64_t K) {
             const int64_t rounds = (tiles * ks + sms - 1) / sms;
             int64_t cost = rounds * ((nks + ks - 1) / ks + unit_fixed) * kT1000[i];
             if (ks > 1) cost += 3000 + (int64_t)ks * M * N * 8 / 5000;       // reduction: launch + partials written and read (~5 MB per stage time)
-            if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = {bn, ks}; }
+            if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = {bn, ks, false}; }
         }
     }
     return best;
 }
-int pick_bn(int64_t M, int64_t N, int64_t K) { return pick_plan(M, N, K).bn; }
 int pick_ksplit(int64_t M, int64_t N, int64_t K) { return pick_plan(M, N, K).ksplit; }
 
 // Tile width of the cta_group::2 kernel (gemm_mxf4_pair.cu), or 0 for the one-CTA kernel.  Measured on B200 against the
@@ -662,18 +679,20 @@ int gemm_run(const uint8_t* a_packed, const uint8_t* a_sf_blocked, const uint8_t
     }
     CUtensorMap mw, mx;
     const int pair_bn = pick_pair_bn(M, N, mode == MXFP4_GEMM_EXACT);            // 0: one-CTA kernel
-    const int bn = pair_bn ? pair_bn : pick_bn(M, N, K);
-    int rc = make_map(&mw, w_packed, N, K / 2, kTileW);
+    const TilePlan plan = pick_plan(M, N, K);
+    const bool swap = !pair_bn && plan.swap;                                     // activations on the MMA's M side
+    const int bn = pair_bn ? pair_bn : plan.bn;
+    int rc = make_map(&mw, w_packed, N, K / 2, swap ? 256 : kTileW);
     if (rc) return rc;
-    rc = make_map(&mx, a_packed, M, K / 2, pair_bn ? pair_bn / 2 : bn);
+    rc = make_map(&mx, a_packed, M, K / 2, swap ? 128 : (pair_bn ? pair_bn / 2 : bn));
     if (rc) return rc;
     GemmParams p;
     p.sfw = w_sf_prepared; p.sfx = a_sf_blocked; p.bias = (const __nv_bfloat16*)bias_bf16; p.out = (__nv_bfloat16*)out_bf16;
     p.partial = nullptr;
     p.ldo = ldo; p.M = (int)M; p.N = (int)N; p.K = (int)K; p.kstages = (int)((K + kStageK - 1) / kStageK);
-    p.n_tiles = (int)((N + kTileW - 1) / kTileW); p.m_tiles = 0;
+    p.n_tiles = swap ? (int)((N + 255) / 256) : (int)((N + kTileW - 1) / kTileW); p.m_tiles = 0;
     p.ksplit = 1;
-    const int want = pair_bn ? 1 : pick_ksplit(M, N, K);
+    const int want = pair_bn ? 1 : plan.ksplit;
     if (want > 1 && splitk_workspace != nullptr && splitk_bytes >= (int64_t)want * M * N * 4 && (uintptr_t)splitk_workspace % 16 == 0) {
         p.ksplit = want;
         p.partial = (float*)splitk_workspace;
@@ -694,7 +713,8 @@ int gemm_run(const uint8_t* a_packed, const uint8_t* a_sf_blocked, const uint8_t
         if (!p.tma_store) mo = mw;              // any valid map: the kernel does not touch it
         return launch_gemm_pair(pair_bn, mw, mx, mo, p, st);
     }
-    switch (bn) {
+    if (swap) rc = launch_gemm_swap(mw, mx, p, st);
+    else switch (bn) {
         case 32: rc = launch_gemm<32>(mw, mx, p, st); break;
         case 64: rc = launch_gemm<64>(mw, mx, p, st); break;
         case 128: rc = launch_gemm<128>(mw, mx, p, st); break;

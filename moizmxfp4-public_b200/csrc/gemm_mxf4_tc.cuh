@@ -28,6 +28,10 @@ struct GemmParams {
 // map_out: bf16 [M, ldo] with 32 x 32 boxes; used when p.tma_store is set
 int launch_gemm_pair(int bn, const CUtensorMap& map_w, const CUtensorMap& map_x, const CUtensorMap& map_out, GemmParams& p, cudaStream_t stream);
 
+// kernel with the activations on the MMA's M side (gemm_mxf4_swap.cu), for M <= 128: map_w holds 256-row boxes, map_x
+// 128-row boxes, p.n_tiles counts 256-row weight tiles
+int launch_gemm_swap(const CUtensorMap& map_w, const CUtensorMap& map_x, GemmParams& p, cudaStream_t stream);
+
 namespace {
 
 constexpr int kTileW = 128;         // weight rows per CTA (MMA M)

@@ -289,6 +289,54 @@ def test_pair_kernel_equals_one_cta_kernel(monkeypatch, M, N, K, bn, mode):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("M,N,K,ksplit", [(128, 22016, 4096, 0), (128, 512, 256, 1), (1, 256, 32, 1), (37, 1001, 2080, 2), (64, 4096, 4096, 4),
+                                           (128, 300, 544, 1), (100, 11008, 4096, 3)])
+@pytest.mark.parametrize("mode", ["exact", "fast"])
+def test_kernel_with_activations_on_the_m_side(monkeypatch, M, N, K, ksplit, mode):
+    """The decode-sized kernel with exchanged operand roles (256 weight rows on the MMA's N side) against the standard
+    one-CTA kernel and the operand-matched oracle: ragged M / N / K, a last tile with a single 128-row scale tile, bias,
+    K ranges with float32 partial sums, an output view with an odd pitch.  ksplit 0 = the library's own choice, which
+    takes this kernel for [128, 22016, 4096] without being forced."""
+    import mxfp4
+    from mxfp4 import gemm
+    dev = torch.device("cuda", 0)
+    w = weight(N, K, 3, True)
+    packed, scales = mxfp4.MXFP4Quantizer(32, "e8m0").quantize(w.to(dev))
+    hx = act(M, K, 11)
+    x = hx.to(dev)
+    bias = (torch.randn(N, generator=torch.Generator().manual_seed(2)) * 0.1).to(torch.bfloat16)
+    old = gemm.get_gemm_mode()
+    gemm.set_gemm_mode(mode)
+    try:
+        if ksplit:
+            monkeypatch.setenv("MXFP4_GEMM_KSPLIT", str(ksplit))
+        monkeypatch.setenv("MXFP4_GEMM_SWAP", "0")
+        want = gemm.quant_matmul_2d(x, packed, scales, bias.to(dev))
+        if ksplit:
+            monkeypatch.setenv("MXFP4_GEMM_SWAP", "1")
+        else:
+            monkeypatch.delenv("MXFP4_GEMM_SWAP")
+        got = gemm.quant_matmul_2d(x, packed, scales, bias.to(dev))
+        wide = torch.zeros(M, N + 3, dtype=torch.bfloat16, device=dev)          # pitch not a multiple of 16 bytes
+        gemm.quant_matmul_2d(x, packed, scales, bias.to(dev), out=wide[:, :N])
+        torch.cuda.synchronize()
+        gemm.check_status()
+    finally:
+        gemm.set_gemm_mode(old)
+    assert torch.equal(wide[:, :N].contiguous().view(torch.int16), got.view(torch.int16))
+    assert float(wide[:, N:].abs().max()) == 0.0
+    same = torch.equal(got.view(torch.int16), want.view(torch.int16))
+    diff = rel_fro(got.float().cpu(), want.float().cpu())
+    print(f"M={M} N={N} K={K} {mode}: bit-identical to the standard kernel: {same}; rel_fro between the two {diff:.2e}")
+    assert diff < 2e-3
+    if mode == "exact":
+        rows = torch.arange(M)[:: max(1, M // 16)]
+        op, os_ = packed.cpu(), scales.cpu()
+        ref = oracle.matmul_operand_matched(hx[rows], op, os_, bias).float()
+        assert rel_fro(got[rows.to(dev)].float().cpu(), ref) <= TOL
+
+
+@pytest.mark.gpu
 @pytest.mark.parametrize("world", [2, 4, 8])
 def test_peer_allreduce_single_gpu_and_bounded_wait(monkeypatch, world):
     """mxfp4_peer_allreduce with all 'ranks' emulated by buffers of one GPU (rank 0 runs; the others are data).  First the
